@@ -1,0 +1,80 @@
+"""ctypes binding of ``libaarambh_b200.so`` (the C ABI in ``include/aarambh_b200.h``).
+
+The library is the only compute path: importing this module without the built
+shared object raises, and nothing here falls back to PyTorch or the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libaarambh_b200.so")
+
+OK = 0
+F32, F16, BF16 = 0, 1, 2
+KV_F32, KV_BF16, KV_INT8 = 0, 1, 2
+FMT_I8, FMT_I4_AFFINE, FMT_Q4KM, FMT_W4A16 = 0, 1, 2, 3
+
+STATUS_NAMES = {
+    0: "OK", -1: "BAD_SHAPE", -2: "BAD_ALIGN", -3: "BAD_DTYPE", -4: "CAPACITY", -5: "CUDA_ERROR",
+    -6: "TIMEOUT", -7: "BAD_ARG", -8: "UNSUPPORTED",
+}
+
+
+class Ab2Error(RuntimeError):
+    """A failed library call; ``status`` is the ab2_status code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python aarambh-ai_b200/build.py` "
+        "(there is no fallback path)")
+
+lib = C.CDLL(LIB_PATH)
+
+_p = C.c_void_p
+_i = C.c_int
+_f = C.c_float
+_pp = C.POINTER(C.c_void_p)
+
+# name -> (argtypes, restype); every symbol declared in include/aarambh_b200.h.
+SIGNATURES = {
+    "ab2_version": ([], _i),
+    "ab2_last_error": ([], C.c_char_p),
+    "ab2_qweight_from_i8_tensor": ([_pp, _p, _f, _i, _i], _i),
+    "ab2_qweight_from_i8_channel": ([_pp, _p, _p, _i, _i], _i),
+    "ab2_qweight_from_i4_affine": ([_pp, _p, _p, _p, _i, _i, _i], _i),
+    "ab2_qweight_from_q4km_blocks": ([_pp, _p, _i, _i], _i),
+    "ab2_qweight_from_w4a16_gptq": ([_pp, _p, _p, _p, _i, _i, _i], _i),
+    "ab2_qweight_from_w4a16_awq": ([_pp, _p, _p, _p, _i, _i, _i], _i),
+    "ab2_qweight_quantise_i8": ([_pp, _p, _i, _i, _i, _p], _i),
+    "ab2_qweight_quantise_i4_affine": ([_pp, _p, _i, _i, _i, _p], _i),
+    "ab2_qweight_quantise_q4km": ([_pp, _p, _i, _i, _p], _i),
+    "ab2_qweight_quantise_w4a16": ([_pp, _p, _i, _i, _i, _p], _i),
+    "ab2_qweight_destroy": ([_p], _i),
+    "ab2_qweight_shape": ([_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)], _i),
+    "ab2_qweight_nbytes": ([_p, C.POINTER(C.c_size_t)], _i),
+    "ab2_qweight_export": ([_p, _p, _p, _p], _i),
+    "ab2_qweight_dequant": ([_p, _p, _i, _p], _i),
+    "ab2_qlinear_forward": ([_p, _p, _i, _i, _p, _p], _i),
+}
+
+
+def _declare():
+    for name, (argtypes, restype) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = restype
+
+
+_declare()
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise Ab2Error(status, lib.ab2_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,87 @@
+"""QatLinear::forward parity: fused dequant + contraction against the oracle's
+dequantise-then-matmul (crates/aarambh-studio-quant/src/qat.rs:315-348).
+Tolerance: 1e-2 relative (max |diff| / max |ref|), the bar stated for linear
+outputs; f32 activations are held to 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import make_w4a16, pkg, rel_err
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 1e-2
+TOL_F32 = 1e-5
+
+
+def run(lin, x, dtype):
+    xt = torch.from_numpy(x).cuda().to(dtype)
+    return lin(xt).float().cpu().numpy()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 16])
+@pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 384)])
+def test_w4a16_gptq_linear(M, K, N):
+    rng = np.random.default_rng(2)
+    qw, scales, qz = make_w4a16(rng, N, K)
+    lin = pkg().QuantLinear.from_w4a16_gptq(qw, scales, qz, N, K, 128)
+    dense = orc.dequant_w4a16(qw, scales, qz, N, K, 128)
+    x = orc.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    ref = orc.linear(x, dense)
+    assert rel_err(run(lin, x, torch.bfloat16), ref) < TOL_BF16
+    assert rel_err(run(lin, x, torch.float32), ref) < TOL_F32
+
+
+@pytest.mark.parametrize("M", [1, 5])
+def test_w4a16_awq_linear(M):
+    rng = np.random.default_rng(3)
+    N, K = 384, 2048
+    qw, scales, qz = make_w4a16(rng, N, K, awq=True)
+    lin = pkg().QuantLinear.from_w4a16_awq(qw, scales, qz, N, K, 128)
+    dense = orc.dequant_w4a16(qw, scales, qz, N, K, 128, awq_order=True)
+    x = orc.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    assert rel_err(run(lin, x, torch.bfloat16), orc.linear(x, dense)) < TOL_BF16
+
+
+@pytest.mark.parametrize("method", ["int8", "int8_channel", "int4", "q4_k_m"])
+@pytest.mark.parametrize("K,N", [(384, 384), (384, 128), (1024, 384), (384, 8192)])
+@pytest.mark.parametrize("M", [1, 32])
+def test_reference_formats_f32_linear(method, K, N, M):
+    """The Tiny model's projection shapes in the reference's own formats."""
+    rng = np.random.default_rng(4)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    lin = pkg().QuantLinear.quantise(torch.from_numpy(w).cuda(), method, 128)
+    dense = lin.dequantise().cpu().numpy()
+    if method == "int8":
+        codes, scale = orc.quantise_absmax_i8(w)
+        assert np.array_equal(dense, orc.dequantise_i8(codes, scale))
+    elif method == "q4_k_m":
+        assert np.array_equal(dense, orc.decode_q4km_tensor(orc.encode_q4km_tensor(w), (N, K)))
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    ref = orc.linear(x, dense)
+    assert rel_err(run(lin, x, torch.float32), ref) < TOL_F32
+    xb = orc.round_bf16(x)
+    assert rel_err(run(lin, xb, torch.bfloat16), orc.linear(xb, dense)) < TOL_BF16
+
+
+def test_leading_dimensions_are_flattened():
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((64, 128)) * 0.02).astype(np.float32)
+    lin = pkg().QuantLinear.quantise(torch.from_numpy(w).cuda(), "int8")
+    x = torch.from_numpy(rng.standard_normal((2, 3, 128)).astype(np.float32)).cuda()
+    y = lin(x)
+    assert tuple(y.shape) == (2, 3, 64)
+    assert torch.allclose(y.view(6, 64), lin(x.view(6, 128)))
+
+
+def test_shape_and_dtype_errors():
+    p = pkg()
+    w = torch.zeros(8, 64, device="cuda")
+    lin = p.QuantLinear.quantise(w, "int8")
+    with pytest.raises(p.Ab2Error) as e:
+        lin(torch.zeros(2, 32, device="cuda"))
+    assert e.value.status == -1
+    with pytest.raises(p.Ab2Error) as e:
+        lin(torch.zeros(2, 64, device="cuda", dtype=torch.float64))
+    assert e.value.status == -3
