@@ -46,6 +46,7 @@ _pp = C.POINTER(C.c_void_p)
 SIGNATURES = {
     "ab2_version": ([], _i),
     "ab2_last_error": ([], C.c_char_p),
+    "ab2_device_status": ([C.POINTER(_i)], _i),
     "ab2_qweight_from_i8_tensor": ([_pp, _p, _f, _i, _i], _i),
     "ab2_qweight_from_i8_channel": ([_pp, _p, _p, _i, _i], _i),
     "ab2_qweight_from_i4_affine": ([_pp, _p, _p, _p, _i, _i, _i], _i),
@@ -78,3 +79,10 @@ _declare()
 def check(status: int) -> None:
     if status != OK:
         raise Ab2Error(status, lib.ab2_last_error().decode("utf-8", "replace"))
+
+
+def device_status() -> int:
+    """Synchronises and returns the device status word (0, or a negative ab2_status)."""
+    out = C.c_int(0)
+    check(lib.ab2_device_status(C.byref(out)))
+    return out.value

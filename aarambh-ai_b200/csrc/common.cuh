@@ -44,7 +44,7 @@ enum Format : int {
     FMT_I8 = 0,         // int8 codes [N][K], f32 scale per row
     FMT_I4_AFFINE = 1,  // nibbles [N*K/2], f32 scale + f32 zero per flat group
     FMT_Q4KM = 2,       // nibbles [ceil(N*K/256)*128], (f16 scale, f16 min) per 256-block
-    FMT_W4A16 = 3       // u32 [N][K/8], bf16 scale [N][G], u4 zero packed [N][G/8]
+    FMT_W4A16 = 3       // tile-major blocks of code and parameter words (w4a16_layout.cuh)
 };
 
 }  // namespace ab2
@@ -58,8 +58,6 @@ struct ab2_qweight {
     float *scales;         // FMT_I8: [N]; FMT_I4_AFFINE: [ngroups]
     float *zeros;          // FMT_I4_AFFINE: [ngroups]
     uint32_t *block_params;  // FMT_Q4KM: lo16 = f16 scale, hi16 = f16 min, per block
-    uint16_t *scales16;    // FMT_W4A16: bf16 [N][G]
-    uint32_t *qzeros;      // FMT_W4A16: [N][G/8]
     size_t codes_bytes, param_bytes;
 };
 

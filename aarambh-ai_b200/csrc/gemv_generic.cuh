@@ -8,14 +8,14 @@
 #pragma once
 
 #include "common.cuh"
+#include "w4a16_layout.cuh"
 
 namespace ab2 {
 
 struct GemvArgs {
     const void *codes;
     const float *scales, *zeros;
-    const uint32_t *block_params, *qzeros;
-    const uint16_t *scales16;
+    const uint32_t *block_params;
     int N, K, group;
 };
 
@@ -64,6 +64,18 @@ __device__ __forceinline__ void dequant_word(const GemvArgs &a, int n, int word,
             int8_t code = (int8_t)((r[j >> 2] >> (8 * (j & 3))) & 0xff);
             w[j] = __fmul_rn((float)code, s);
         }
+    } else if constexpr (FMT == FMT_W4A16) {
+        W4Layout L{a.N, a.K, a.group};
+        const uint32_t *t = (const uint32_t *)a.codes;
+        uint32_t raw = t[L.code_index(n, word)];
+        uint32_t p = t[L.param_index(n, (word * 8) / a.group)];
+        float s = bf16_bits_to_f32((uint16_t)(p & 0xffffu));
+        float z = (float)((p >> 16) & 0xFu);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {  // interleaved slots: element j sits in slot j/2 + 4*(j&1)
+            int slot = (j >> 1) + 4 * (j & 1);
+            w[j] = __fmul_rn(__fsub_rn((float)((raw >> (4 * slot)) & 0xFu), z), s);
+        }
     } else {
         size_t flat = (size_t)n * a.K + (size_t)word * 8;
         uint32_t raw = ((const uint32_t *)a.codes)[flat >> 3];
@@ -80,14 +92,6 @@ __device__ __forceinline__ void dequant_word(const GemvArgs &a, int n, int word,
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 w[j] = __fadd_rn(__fmul_rn((float)((raw >> (4 * j)) & 0xFu), s), m);
-        } else {  // FMT_W4A16
-            int G = a.K / a.group, g = (word * 8) / a.group;
-            size_t gi = (size_t)n * G + g;
-            float s = bf16_bits_to_f32(a.scales16[gi]);
-            float z = (float)((a.qzeros[gi >> 3] >> (4 * (g & 7))) & 0xFu);
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                w[j] = __fmul_rn(__fsub_rn((float)((raw >> (4 * j)) & 0xFu), z), s);
         }
     }
 }

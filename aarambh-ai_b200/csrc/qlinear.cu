@@ -1,6 +1,9 @@
 // QatLinear::forward over packed weights: shape checks and kernel selection.
+#include <algorithm>
+
 #include "common.cuh"
 #include "gemv_generic.cuh"
+#include "gemv_w4a16_mma.cuh"
 
 using namespace ab2;
 
@@ -9,7 +12,7 @@ namespace ab2 {
 GemvArgs gemv_args_of(const ab2_qweight *w) {
     GemvArgs a;
     a.codes = w->codes; a.scales = w->scales; a.zeros = w->zeros;
-    a.block_params = w->block_params; a.qzeros = w->qzeros; a.scales16 = w->scales16;
+    a.block_params = w->block_params;
     a.N = w->N; a.K = w->K; a.group = w->group;
     return a;
 }
@@ -64,11 +67,70 @@ int qlinear_generic(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype,
     }
 }
 
+// Per-device status word written by kernels whose bounded waits ran out.
+static int *g_status_word[64] = {nullptr};
+static int g_sm_count[64] = {0};
+
+int device_status_word(int **out) {
+    int dev = 0;
+    AB2_CUDA(cudaGetDevice(&dev));
+    AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
+    if (!g_status_word[dev]) {
+        AB2_CUDA(cudaMalloc((void **)&g_status_word[dev], sizeof(int)));
+        AB2_CUDA(cudaMemset(g_status_word[dev], 0, sizeof(int)));
+        AB2_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
+    }
+    *out = g_status_word[dev];
+    return AB2_OK;
+}
+
+int device_sm_count() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return (dev >= 0 && dev < 64 && g_sm_count[dev] > 0) ? g_sm_count[dev] : 148;
+}
+
+// Tensor-core decode GEMV: W4A16, group 128, bf16 activations.
+bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype) {
+    return w->fmt == FMT_W4A16 && w->group == 128 && dtype == AB2_BF16;
+}
+
+int qlinear_w4a16_mma(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+    int *status = nullptr;
+    int rc = device_status_word(&status);
+    if (rc != AB2_OK) return rc;
+    const int tiles = (w->N + 15) / 16;
+    const int grid = std::min(tiles, device_sm_count() * 4);
+    const uint32_t *wt = (const uint32_t *)w->codes;
+    for (int m0 = 0; m0 < M; m0 += 16) {
+        const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;
+        __nv_bfloat16 *yp = (__nv_bfloat16 *)y + (size_t)m0 * w->N;
+        int mv = M - m0 < 16 ? M - m0 : 16;
+        if (mv <= 8) gemv_w4a16_stream_kernel<1><<<grid, 256, 0, s>>>(wt, xp, yp, w->N, w->K, mv, status);
+        else gemv_w4a16_stream_kernel<2><<<grid, 256, 0, s>>>(wt, xp, yp, w->N, w->K, mv, status);
+    }
+    AB2_LAUNCH_CHECK();
+    return AB2_OK;
+}
+
 }  // namespace ab2
 
 AB2_API int ab2_qlinear_forward(const ab2_qweight *w, const void *x_dev, int M, ab2_dtype dtype,
                                 void *y_dev, ab2_stream stream) {
     int rc = qlinear_validate(w, x_dev, M, dtype, y_dev);
     if (rc != AB2_OK) return rc;
+    if (qlinear_w4a16_mma_eligible(w, dtype))
+        return qlinear_w4a16_mma(w, x_dev, M, y_dev, (cudaStream_t)stream);
     return qlinear_generic(w, x_dev, M, dtype, y_dev, (cudaStream_t)stream);
+}
+
+AB2_API int ab2_device_status(int *status_host) {
+    AB2_REQUIRE(status_host != nullptr, AB2_ERR_BAD_ARG, "null argument");
+    int *word = nullptr;
+    int rc = device_status_word(&word);
+    if (rc != AB2_OK) return rc;
+    AB2_CUDA(cudaDeviceSynchronize());
+    AB2_CUDA(cudaMemcpy(status_host, word, sizeof(int), cudaMemcpyDeviceToHost));
+    AB2_CUDA(cudaMemset(word, 0, sizeof(int)));
+    return AB2_OK;
 }

@@ -5,6 +5,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "w4a16_layout.cuh"
 
 namespace ab2 {
 
@@ -64,7 +65,7 @@ static int dev_alloc(void **p, size_t bytes) {
 AB2_API int ab2_qweight_destroy(ab2_qweight *w) {
     if (!w) return AB2_OK;
     cudaFree(w->codes); cudaFree(w->scales); cudaFree(w->zeros);
-    cudaFree(w->block_params); cudaFree(w->scales16); cudaFree(w->qzeros);
+    cudaFree(w->block_params);
     delete w;
     return AB2_OK;
 }
@@ -215,28 +216,72 @@ AB2_API int ab2_qweight_from_q4km_blocks(ab2_qweight **out, const uint8_t *block
 static int make_w4a16(ab2_qweight **out, int N, int K, int group) {
     AB2_REQUIRE(group > 0 && group % 8 == 0, AB2_ERR_BAD_SHAPE, "group size must be a positive multiple of 8, got %d", group);
     AB2_REQUIRE(K % group == 0, AB2_ERR_BAD_SHAPE, "K=%d is not a multiple of the group size %d", K, group);
-    AB2_REQUIRE((K / group) % 8 == 0, AB2_ERR_BAD_SHAPE, "K/group=%d must be a multiple of 8 (packed zero points)", K / group);
     TRY(alloc_handle(out, FMT_W4A16, N, K, group));
     ab2_qweight *w = *out;
-    size_t G = (size_t)K / group;
-    w->codes_bytes = (size_t)N * K / 2;
-    w->param_bytes = (size_t)N * G * 2 + (size_t)N * G / 2;
-    TRY_OR_FREE(w, dev_alloc(&w->codes, w->codes_bytes));
-    TRY_OR_FREE(w, dev_alloc((void **)&w->scales16, (size_t)N * G * 2));
-    TRY_OR_FREE(w, dev_alloc((void **)&w->qzeros, (size_t)N * G / 2));
+    W4Layout L{N, K, group};
+    w->codes_bytes = (size_t)L.tiles() * 16 * K / 2;
+    w->param_bytes = (size_t)L.tiles() * 16 * L.G() * 4;
+    TRY_OR_FREE(w, dev_alloc(&w->codes, L.total_words() * 4));
+    cudaError_t e = cudaMemset(w->codes, 0, L.total_words() * 4);
+    if (e != cudaSuccess) { ab2_qweight_destroy(w); *out = nullptr; return fail(AB2_ERR_CUDA, "cudaMemset failed: %s", cudaGetErrorString(e)); }
     return AB2_OK;
 }
 
-// Rewrites words from the interleaved slot order (slot i holds element
-// {0,2,4,6,1,3,5,7}[i]) to the natural order (slot j holds element j).
-__global__ void awq_to_natural_kernel(uint32_t *words, size_t n) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    uint32_t v = words[i], o = 0;
+// Input layout [N][K/8] code words (natural or interleaved nibble order),
+// scales [N][G] bf16, zero points [N][ceil(G/8)] -> tile-major blocks.
+__device__ __forceinline__ uint32_t w4_to_interleaved(uint32_t v) {
     const int slot_of[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+    uint32_t o = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o |= ((v >> (4 * e)) & 0xFu) << (4 * slot_of[e]);
+    return o;
+}
+__device__ __forceinline__ uint32_t w4_to_natural(uint32_t v) {
+    const int slot_of[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+    uint32_t o = 0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) o |= ((v >> (4 * slot_of[e])) & 0xFu) << (4 * e);
-    words[i] = o;
+    return o;
+}
+
+__global__ void w4a16_tile_codes_kernel(const uint32_t *qweight, W4Layout L, bool awq,
+                                        uint32_t *tiles) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t wpr = (size_t)L.K >> 3;
+    if (i >= (size_t)L.N * wpr) return;
+    int n = (int)(i / wpr), word = (int)(i % wpr);
+    uint32_t v = qweight[i];
+    tiles[L.code_index(n, word)] = awq ? v : w4_to_interleaved(v);
+}
+
+__global__ void w4a16_tile_params_kernel(const uint16_t *scales16, const uint32_t *qzeros,
+                                         W4Layout L, bool awq, uint32_t *tiles) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int G = L.G();
+    if (i >= (size_t)L.N * G) return;
+    int n = (int)(i / G), g = (int)(i % G);
+    int e = g & 7, slot = awq ? (e >> 1) + 4 * (e & 1) : e;
+    uint32_t z = (qzeros[(size_t)n * ((G + 7) >> 3) + (g >> 3)] >> (4 * slot)) & 0xFu;
+    tiles[L.param_index(n, g)] = (uint32_t)scales16[i] | ((0xC300u | z) << 16);
+}
+
+// tile-major blocks -> natural-order [N][K/8] words, scales, zero points
+__global__ void w4a16_untile_codes_kernel(const uint32_t *tiles, W4Layout L, uint32_t *qweight) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t wpr = (size_t)L.K >> 3;
+    if (i >= (size_t)L.N * wpr) return;
+    qweight[i] = w4_to_natural(tiles[L.code_index((int)(i / wpr), (int)(i % wpr))]);
+}
+
+__global__ void w4a16_untile_params_kernel(const uint32_t *tiles, W4Layout L, uint16_t *scales16,
+                                           uint32_t *qzeros) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int G = L.G();
+    if (i >= (size_t)L.N * G) return;
+    int n = (int)(i / G), g = (int)(i % G);
+    uint32_t p = tiles[L.param_index(n, g)];
+    scales16[i] = (uint16_t)(p & 0xffffu);
+    atomicOr(&qzeros[(size_t)n * ((G + 7) >> 3) + (g >> 3)], ((p >> 16) & 0xFu) << (4 * (g & 7)));
 }
 
 static int from_w4a16(ab2_qweight **out, const uint32_t *qweight, const uint16_t *scales_bf16,
@@ -244,16 +289,22 @@ static int from_w4a16(ab2_qweight **out, const uint32_t *qweight, const uint16_t
     AB2_REQUIRE(qweight && scales_bf16 && qzeros, AB2_ERR_BAD_ARG, "null input pointer");
     TRY(make_w4a16(out, N, K, group));
     ab2_qweight *w = *out;
-    size_t G = (size_t)K / group;
-    cudaError_t e = cudaMemcpy(w->codes, qweight, w->codes_bytes, cudaMemcpyDefault);
-    if (e == cudaSuccess) e = cudaMemcpy(w->scales16, scales_bf16, (size_t)N * G * 2, cudaMemcpyDefault);
-    if (e == cudaSuccess) e = cudaMemcpy(w->qzeros, qzeros, (size_t)N * G / 2, cudaMemcpyDefault);
-    if (e == cudaSuccess && awq) {
-        size_t nw = (size_t)N * K / 8, nz = (size_t)N * G / 8;
-        awq_to_natural_kernel<<<(unsigned)ceil_div(nw, 256), 256>>>((uint32_t *)w->codes, nw);
-        awq_to_natural_kernel<<<(unsigned)ceil_div(nz, 256), 256>>>(w->qzeros, nz);
+    W4Layout L{N, K, group};
+    size_t G = (size_t)L.G(), ZW = ceil_div(G, 8), nw = (size_t)N * K / 8;
+    uint32_t *c_dev = nullptr, *z_dev = nullptr;
+    uint16_t *s_dev = nullptr;
+    cudaError_t e = cudaMalloc((void **)&c_dev, nw * 4);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&s_dev, (size_t)N * G * 2);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&z_dev, (size_t)N * ZW * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(c_dev, qweight, nw * 4, cudaMemcpyDefault);
+    if (e == cudaSuccess) e = cudaMemcpy(s_dev, scales_bf16, (size_t)N * G * 2, cudaMemcpyDefault);
+    if (e == cudaSuccess) e = cudaMemcpy(z_dev, qzeros, (size_t)N * ZW * 4, cudaMemcpyDefault);
+    if (e == cudaSuccess) {
+        w4a16_tile_codes_kernel<<<(unsigned)ceil_div(nw, 256), 256>>>(c_dev, L, awq, (uint32_t *)w->codes);
+        w4a16_tile_params_kernel<<<(unsigned)ceil_div((size_t)N * G, 256), 256>>>(s_dev, z_dev, L, awq, (uint32_t *)w->codes);
+        e = cudaDeviceSynchronize();
     }
-    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaFree(c_dev); cudaFree(s_dev); cudaFree(z_dev);
     if (e != cudaSuccess) { ab2_qweight_destroy(w); *out = nullptr; return fail(AB2_ERR_CUDA, "W4A16 weight upload failed: %s", cudaGetErrorString(e)); }
     return AB2_OK;
 }
@@ -297,11 +348,24 @@ AB2_API int ab2_qweight_export(const ab2_qweight *w, void *codes, void *scales, 
         }
         break;
     }
-    case FMT_W4A16: {
-        size_t G = (size_t)w->K / w->group;
-        if (codes) AB2_CUDA(cudaMemcpy(codes, w->codes, w->codes_bytes, cudaMemcpyDefault));
-        if (scales) AB2_CUDA(cudaMemcpy(scales, w->scales16, (size_t)w->N * G * 2, cudaMemcpyDefault));
-        if (zeros) AB2_CUDA(cudaMemcpy(zeros, w->qzeros, (size_t)w->N * G / 2, cudaMemcpyDefault));
+    case FMT_W4A16: {  // exported in the natural (GPTQ) nibble order
+        W4Layout L{w->N, w->K, w->group};
+        size_t G = (size_t)L.G(), ZW = ceil_div(G, 8), nw = (size_t)w->N * w->K / 8, NG = (size_t)w->N * G;
+        uint32_t *c_dev = nullptr, *z_dev = nullptr;
+        uint16_t *s_dev = nullptr;
+        cudaError_t e = cudaMalloc((void **)&c_dev, nw * 4);
+        if (e == cudaSuccess) e = cudaMalloc((void **)&s_dev, NG * 2);
+        if (e == cudaSuccess) e = cudaMalloc((void **)&z_dev, (size_t)w->N * ZW * 4);
+        if (e == cudaSuccess) e = cudaMemset(z_dev, 0, (size_t)w->N * ZW * 4);
+        if (e == cudaSuccess) {
+            w4a16_untile_codes_kernel<<<(unsigned)ceil_div(nw, 256), 256>>>((const uint32_t *)w->codes, L, c_dev);
+            w4a16_untile_params_kernel<<<(unsigned)ceil_div(NG, 256), 256>>>((const uint32_t *)w->codes, L, s_dev, z_dev);
+            if (codes) e = cudaMemcpy(codes, c_dev, nw * 4, cudaMemcpyDefault);
+            if (e == cudaSuccess && scales) e = cudaMemcpy(scales, s_dev, NG * 2, cudaMemcpyDefault);
+            if (e == cudaSuccess && zeros) e = cudaMemcpy(zeros, z_dev, (size_t)w->N * ZW * 4, cudaMemcpyDefault);
+        }
+        cudaFree(c_dev); cudaFree(s_dev); cudaFree(z_dev);
+        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "W4A16 export failed: %s", cudaGetErrorString(e));
         break;
     }
     default:
@@ -317,15 +381,14 @@ struct QView {
     int fmt, N, K, group;
     const void *codes;
     const float *scales, *zeros;
-    const uint32_t *block_params, *qzeros;
-    const uint16_t *scales16;
+    const uint32_t *block_params;
 };
 
 static QView view_of(const ab2_qweight *w) {
     QView v;
     v.fmt = w->fmt; v.N = w->N; v.K = w->K; v.group = w->group;
     v.codes = w->codes; v.scales = w->scales; v.zeros = w->zeros;
-    v.block_params = w->block_params; v.qzeros = w->qzeros; v.scales16 = w->scales16;
+    v.block_params = w->block_params;
     return v;
 }
 
@@ -352,11 +415,14 @@ __device__ __forceinline__ float dequant_element(const QView &v, size_t idx) {
     }
     default: {  // FMT_W4A16: (q - z) * s with bf16 s, u4 z widened to f32
         int n = (int)(idx / v.K), k = (int)(idx % v.K);
-        int G = v.K / v.group, g = k / v.group;
-        uint32_t word = ((const uint32_t *)v.codes)[idx >> 3];
-        float q = (float)((word >> (4 * (k & 7))) & 0xFu);
-        float z = (float)((v.qzeros[((size_t)n * G + g) >> 3] >> (4 * (g & 7))) & 0xFu);
-        float s = bf16_bits_to_f32(v.scales16[(size_t)n * G + g]);
+        int g = k / v.group;
+        W4Layout L{v.N, v.K, v.group};
+        uint32_t word = ((const uint32_t *)v.codes)[L.code_index(n, k >> 3)];
+        int e = k & 7, slot = (e >> 1) + 4 * (e & 1);
+        float q = (float)((word >> (4 * slot)) & 0xFu);
+        uint32_t p = ((const uint32_t *)v.codes)[L.param_index(n, g)];
+        float z = (float)((p >> 16) & 0xFu);
+        float s = bf16_bits_to_f32((uint16_t)(p & 0xffffu));
         return __fmul_rn(__fsub_rn(q, z), s);
     }
     }
@@ -595,8 +661,8 @@ AB2_API int ab2_qweight_quantise_q4km(ab2_qweight **out, const float *w_dev, int
 
 // One warp per (row, group).  The stored scale is the bf16 rounding of the
 // int4.rs scale; zero point and codes are derived from the stored scale.
-__global__ void w4a16_quantise_kernel(const float *w, int N, int K, int group, uint32_t *codes,
-                                      uint16_t *scales16, uint32_t *qzeros) {
+__global__ void w4a16_quantise_kernel(const float *w, int N, int K, int group, uint32_t *tiles) {
+    W4Layout L{N, K, group};
     int G = K / group;
     size_t wg = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (wg >= (size_t)N * G) return;
@@ -615,19 +681,18 @@ __global__ void w4a16_quantise_kernel(const float *w, int N, int K, int group, u
     __nv_bfloat16 sb = __float2bfloat16_rn(scale);
     float s = __bfloat162float(sb);
     float zero = clamp_f(roundf(__fdiv_rn(-mn, s)), 0.f, 15.f);
-    if (lane == 0) {
-        scales16[wg] = __bfloat16_as_ushort(sb);
-        atomicOr(&qzeros[wg >> 3], ((uint32_t)sat_u8(zero)) << (4 * (g & 7)));
-    }
+    if (lane == 0)
+        tiles[L.param_index(n, g)] =
+            (uint32_t)__bfloat16_as_ushort(sb) | ((0xC300u | (uint32_t)sat_u8(zero)) << 16);
     for (int word = lane; word < group / 8; word += 32) {
         uint32_t packed = 0;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             float v = src[word * 8 + j];
             uint32_t q = sat_u8(clamp_f(roundf(__fadd_rn(__fdiv_rn(v, s), zero)), 0.f, 15.f));
-            packed |= (q & 0xFu) << (4 * j);
+            packed |= (q & 0xFu) << (4 * ((j >> 1) + 4 * (j & 1)));
         }
-        codes[((size_t)n * K + (size_t)g * group) / 8 + word] = packed;
+        tiles[L.code_index(n, g * (group / 8) + word)] = packed;
     }
 }
 
@@ -638,9 +703,8 @@ AB2_API int ab2_qweight_quantise_w4a16(ab2_qweight **out, const float *w_dev, in
     ab2_qweight *w = *out;
     size_t G = (size_t)K / group;
     cudaStream_t s = (cudaStream_t)stream;
-    AB2_CUDA(cudaMemsetAsync(w->qzeros, 0, (size_t)N * G / 2, s));
     w4a16_quantise_kernel<<<(unsigned)ceil_div((size_t)N * G, 8), 256, 0, s>>>(
-        w_dev, N, K, group, (uint32_t *)w->codes, w->scales16, w->qzeros);
+        w_dev, N, K, group, (uint32_t *)w->codes);
     AB2_LAUNCH_CHECK();
     AB2_CUDA(cudaStreamSynchronize(s));
     return AB2_OK;

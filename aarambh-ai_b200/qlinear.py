@@ -154,7 +154,7 @@ class QuantLinear:
             return blocks, None, None
         G = K // g
         codes = np.empty((N, K // 8), np.uint32)
-        scales = np.empty((N, G), np.uint16); zeros = np.empty((N, G // 8), np.uint32)
+        scales = np.empty((N, G), np.uint16); zeros = np.empty((N, -(-G // 8)), np.uint32)
         check(lib.ab2_qweight_export(self._h, codes.ctypes.data, scales.ctypes.data, zeros.ctypes.data))
         return codes, scales, zeros
 

@@ -60,6 +60,10 @@ typedef struct ab2_tp ab2_tp;
 /* ---- library ----------------------------------------------------------- */
 int ab2_version(void);
 const char *ab2_last_error(void);
+/* Synchronises the current device and returns (then clears) its status word:
+ * AB2_OK, or AB2_ERR_TIMEOUT when a kernel's bounded wait ran out.  No
+ * counterpart in the reference, whose kernels never wait on one another. */
+int ab2_device_status(int *status_host);
 
 /* ---- quantised weights --------------------------------------------------
  * An ab2_qweight owns the packed bytes of one [N,K] weight in device memory.
@@ -83,8 +87,8 @@ int ab2_qweight_from_i4_affine(ab2_qweight **out, const uint8_t *packed, const f
  *  crates/aarambh-studio-weights/src/gguf.rs:214-241). */
 int ab2_qweight_from_q4km_blocks(ab2_qweight **out, const uint8_t *blocks132, int N, int K);
 /* W4A16 group-wise layout: qweight [N, K/8] u32 with element k = 8*word + j in
- * bits 4j..4j+3, scales [N, K/group] bf16, qzeros [N, K/group/8] u32 (zero
- * points 0..15, same nibble order along groups).  Dequantisation is
+ * bits 4j..4j+3, scales [N, K/group] bf16, qzeros [N, ceil(K/group/8)] u32 (zero
+ * points 0..15, same nibble order along groups, rows padded to whole words).  Dequantisation is
  * (q - z) * s in f32 (crates/aarambh-studio-quant/src/int4.rs:88). */
 int ab2_qweight_from_w4a16_gptq(ab2_qweight **out, const uint32_t *qweight,
                                 const uint16_t *scales_bf16, const uint32_t *qzeros, int N, int K,

@@ -371,7 +371,7 @@ ORC_API void orc_fake_quant_export_q4km(const float *values, size_t n, float *ou
 /* ------------------------------------------------------------------------- */
 
 /* GPTQ-style: qweight[N][K/8] u32, nibble j of a word (bits 4j..4j+3) is element
- * k = 8*word + j; scales[N][K/group] bf16; qzeros[N][K/group/8] u32 with the same
+ * k = 8*word + j; scales[N][K/group] bf16; qzeros[N][ceil(K/group/8)] u32 with the same
  * nibble order along groups.  Dequant follows int4.rs:88 with the stored
  * parameters widened to f32: (q - z) * s. */
 ORC_API void orc_dequant_w4a16(const uint32_t *qweight, const uint16_t *scales_bf16,
@@ -386,7 +386,7 @@ ORC_API void orc_dequant_w4a16(const uint32_t *qweight, const uint16_t *scales_b
             uint32_t word = qweight[(size_t)n * (K / 8) + k / 8];
             int slot = awq_order ? awq_slot_of[k & 7] : (k & 7);
             float q = (float)((word >> (4 * slot)) & 0xfu);
-            uint32_t zw = qzeros[(size_t)n * (G / 8) + g / 8];
+            uint32_t zw = qzeros[(size_t)n * ((G + 7) / 8) + g / 8];
             int zslot = awq_order ? awq_slot_of[g & 7] : (g & 7);
             float z = (float)((zw >> (4 * zslot)) & 0xfu);
             float s = orc_bf16_to_f32(scales_bf16[(size_t)n * G + g]);

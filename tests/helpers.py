@@ -30,6 +30,8 @@ def pack_w4(codes, order=None):
     """[N, K] nibble values -> [N, K/8] u32 words; slot i holds element order[i]."""
     order = list(range(8)) if order is None else order
     codes = np.ascontiguousarray(codes, np.uint32)
+    if codes.shape[1] % 8:
+        codes = np.pad(codes, ((0, 0), (0, 8 - codes.shape[1] % 8)))
     out = np.zeros((codes.shape[0], codes.shape[1] // 8), np.uint32)
     for slot, elem in enumerate(order):
         out |= codes[:, elem::8] << np.uint32(4 * slot)
