@@ -3,5 +3,8 @@
 Every operator here calls the C ABI of ``libaarambh_b200.so``; importing the
 package without the built library fails (no CPU or PyTorch fallback exists).
 """
-from ._lib import Ab2Error, check, lib  # noqa: F401
+from ._lib import Ab2Error, check, device_status, lib  # noqa: F401
 from .qlinear import QuantLinear  # noqa: F401
+from .kvcache import KVCache  # noqa: F401
+from . import dispatch  # noqa: F401
+from .model import AarambhModel, InferenceEngine, ModelConfig  # noqa: F401

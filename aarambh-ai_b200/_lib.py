@@ -57,13 +57,48 @@ SIGNATURES = {
     "ab2_qweight_quantise_i4_affine": ([_pp, _p, _i, _i, _i, _p], _i),
     "ab2_qweight_quantise_q4km": ([_pp, _p, _i, _i, _p], _i),
     "ab2_qweight_quantise_w4a16": ([_pp, _p, _i, _i, _i, _p], _i),
+    "ab2_qweight_concat_rows": ([_pp, _pp, _i], _i),
     "ab2_qweight_destroy": ([_p], _i),
     "ab2_qweight_shape": ([_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)], _i),
     "ab2_qweight_nbytes": ([_p, C.POINTER(C.c_size_t)], _i),
     "ab2_qweight_export": ([_p, _p, _p, _p], _i),
     "ab2_qweight_dequant": ([_p, _p, _i, _p], _i),
     "ab2_qlinear_forward": ([_p, _p, _i, _i, _p, _p], _i),
+    "ab2_rms_norm": ([_p, _p, _p, _i, _i, _f, _i, _p], _i),
+    "ab2_rope_apply": ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p], _i),
+    "ab2_swiglu": ([_p, _p, _p, C.c_size_t, _i, _p], _i),
+    "ab2_argmax": ([_p, _i, _i, _i, _p, _p], _i),
+    "ab2_embedding_forward": ([_p, _p, _i, _p, _i, _p], _i),
+    "ab2_kv_create": ([_pp, _i, _i, _i, _i, _i, _i, _i], _i),
+    "ab2_kv_destroy": ([_p], _i),
+    "ab2_kv_update": ([_p, _p, _p, _i, _i, _i, _i, _p], _i),
+    "ab2_kv_append": ([_p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p], _i),
+    "ab2_kv_commit": ([_p, _i, _i, _i, _p], _i),
+    "ab2_kv_truncate": ([_p, _i, _i, _p], _i),
+    "ab2_kv_clear": ([_p, _p], _i),
+    "ab2_kv_seq_len": ([_p, _i, C.POINTER(_i)], _i),
+    "ab2_kv_capacity": ([_p, C.POINTER(_i)], _i),
+    "ab2_kv_clone": ([_pp, _p, _p], _i),
+    "ab2_kv_read": ([_p, _i, _i, _p, _p, _p], _i),
+    "ab2_attention_decode": ([_p, _i, _p, _p, _i, _i, _f, _i, _p], _i),
+    "ab2_attention_cached": ([_p, _i, _p, _p, _i, _i, _i, _f, _i, _p], _i),
+    "ab2_attention_causal": ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p], _i),
+    "ab2_model_create": ([_pp, _p, _i, _i], _i),
+    "ab2_model_destroy": ([_p], _i),
+    "ab2_model_set_linear": ([_p, _i, _i, _p], _i),
+    "ab2_model_set_norm": ([_p, _i, _i, _p], _i),
+    "ab2_model_finalize": ([_p], _i),
+    "ab2_model_rope_tables": ([_p, _pp, _pp], _i),
+    "ab2_model_forward": ([_p, _p, _p, _i, _i, _i, _p, _i, _p, _p, _p], _i),
+    "ab2_model_decode_step": ([_p, _p, _p, _i, _i, _p, _p, _p], _i),
 }
+
+
+class ModelConfig(C.Structure):
+    """ab2_model_config."""
+    _fields_ = [("n_layers", _i), ("d_model", _i), ("n_heads", _i), ("n_kv_heads", _i),
+                ("head_dim", _i), ("ffn_hidden", _i), ("vocab", _i), ("max_seq", _i),
+                ("rms_eps", _f), ("rope_theta", C.c_double), ("tied", _i)]
 
 
 def _declare():

@@ -1,0 +1,52 @@
+// KV cache handle and the device-side view kernels receive (internal header).
+#pragma once
+
+#include "common.cuh"
+
+#define AB2_KV_MAX_SPLITS 64
+
+struct ab2_kv {
+    int L, B, cap, kvh, hd, h;
+    int dtype;        // ab2_kv_dtype
+    void *k, *v;      // [L][B][kvh][cap][hd]
+    float *ks, *vs;   // INT8 only: [L][B][kvh][cap]
+    int *lens_dev;    // [B] committed length of each sequence
+    int *lens_host;   // pinned host mirror (authoritative for host-side checks)
+    // scratch of the split-context decode attention
+    float *part_acc;  // [B][h][max_splits][hd]
+    float *part_ml;   // [B][h][max_splits][2]  (running max, running sum)
+    int max_splits;
+};
+
+namespace ab2 {
+
+struct KvView {
+    int B, cap, kvh, hd, dtype;
+    void *k, *v;
+    float *ks, *vs;
+    int *lens;
+};
+
+KvView kv_view(const ab2_kv *kv, int layer);
+
+// Writes S tokens per row at the rows' current lengths (no advance).  k / v
+// element (row, s, head, d) sits at (row * S + s) * in_stride + head * hd + d.
+int kv_append_device(ab2_kv *kv, int layer, const void *k, const void *v, long long in_stride, int S,
+                     int row0, int nrows, ab2_dtype dtype, const float *cos_t, const float *sin_t,
+                     const int *rope_pos, cudaStream_t s);
+int kv_commit_device(ab2_kv *kv, int S, int row0, int nrows, cudaStream_t s);
+
+// Attention of S new queries per row over the cache.  `pending` is the number of
+// appended but not yet committed tokens per row (S during a model step, 0 after
+// a commit): query qi of a row sees cache positions [0, len + pending - S + qi].
+// `len_hint` bounds the context length used to choose the number of splits
+// (pass the capacity when the launch is captured in a graph).
+// q / out element (row, qi, head, d) sits at row*stride_b + qi*stride_s + head*stride_h + d.
+struct AttnStrides {
+    long long q_b, q_s, q_h, o_b, o_s, o_h;
+};
+int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *out, int S, int pending,
+                            int row0, int nrows, float scale, ab2_dtype dtype, AttnStrides st,
+                            int len_hint, cudaStream_t s);
+
+}  // namespace ab2

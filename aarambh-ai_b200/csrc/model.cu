@@ -1,0 +1,382 @@
+// Dense-GQA decoder over packed weights: the device-side counterpart of
+// AarambhModel::{forward_with_cache, forward_decode_batch}
+// (crates/aarambh-studio-model/src/model.rs:508-641), TransformerBlock::forward
+// (crates/aarambh-studio-nn/src/block.rs:331-371), GroupedQueryAttention
+// (crates/aarambh-studio-nn/src/attention.rs:170-288) and SwiGluFfn
+// (crates/aarambh-studio-nn/src/ffn.rs:29-37).  Q/K/V and gate/up share one
+// packed weight each; the one-token step is captured in a CUDA graph.
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <tuple>
+#include <vector>
+
+#include "common.cuh"
+#include "kv_cache.cuh"
+#include "ops.cuh"
+
+using namespace ab2;
+
+namespace ab2 {
+int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s);
+int device_status_word(int **out);
+}
+
+struct LayerWeights {
+    const ab2_qweight *part[7];  // wq wk wv wo gate up down (borrowed)
+    ab2_qweight *wqkv, *wgu;     // fused (owned)
+    float *norm1, *norm2;        // owned, device
+};
+
+struct StepGraph {
+    cudaGraphExec_t exec;
+};
+
+struct ab2_model {
+    ab2_model_config cfg;
+    ab2_dtype dtype;
+    int max_tokens;
+    std::vector<LayerWeights> layers;
+    const ab2_qweight *embedding, *lm_head;
+    float *final_norm;
+    float *cos_t, *sin_t;  // [max_seq][head_dim/2]
+    bool finalized;
+    // workspace, sized for max_tokens
+    void *x, *xn, *qkv, *attn, *proj, *gu, *hid;
+    int *positions;        // [max rows] explicit RoPE offsets
+    int *positions_host;   // pinned
+    std::map<std::tuple<const void *, const void *, int, int, const void *, const void *>, StepGraph> graphs;
+};
+
+namespace ab2 {
+
+// Rotates the query part of the fused QKV activations in place.
+// qkv [tokens][stride]; token t = row * S + s uses position base[row0 + row] + s.
+template <typename T>
+__global__ void rope_q_kernel(T *qkv, long long stride, int heads, int hd, int S, int row0,
+                              const int *__restrict__ base, const float *__restrict__ cos_t,
+                              const float *__restrict__ sin_t, size_t total_pairs) {
+    const int half = hd >> 1;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total_pairs) return;
+    int i = (int)(idx % half);
+    size_t th = idx / half;
+    int head = (int)(th % heads);
+    size_t tok = th / heads;
+    int pos = base[row0 + (int)(tok / S)] + (int)(tok % S);
+    T *p = qkv + tok * stride + (size_t)head * hd;
+    float o1, o2;
+    rope_rotate(to_f32(p[i]), to_f32(p[half + i]), cos_t[(size_t)pos * half + i], sin_t[(size_t)pos * half + i], o1, o2);
+    p[i] = from_f32<T>(o1);
+    p[half + i] = from_f32<T>(o2);
+}
+
+// Copies the last token's row of every sequence: in [nrows][S][d] -> out [nrows][d].
+template <typename T>
+__global__ void gather_last_kernel(const T *in, T *out, int S, int d) {
+    const T *src = in + ((size_t)blockIdx.x * S + (S - 1)) * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)blockIdx.x * d + i] = src[i];
+}
+
+static int launch_rope_q(ab2_model *m, int T, int S, int row0, const int *base, cudaStream_t s) {
+    const ab2_model_config &c = m->cfg;
+    long long stride = (long long)(c.n_heads + 2 * c.n_kv_heads) * c.head_dim;
+    size_t pairs = (size_t)T * c.n_heads * (c.head_dim / 2);
+    unsigned blocks = (unsigned)ceil_div(pairs, 256);
+    switch (m->dtype) {
+    case AB2_F32: rope_q_kernel<float><<<blocks, 256, 0, s>>>((float *)m->qkv, stride, c.n_heads, c.head_dim, S, row0, base, m->cos_t, m->sin_t, pairs); break;
+    case AB2_F16: rope_q_kernel<__half><<<blocks, 256, 0, s>>>((__half *)m->qkv, stride, c.n_heads, c.head_dim, S, row0, base, m->cos_t, m->sin_t, pairs); break;
+    default: rope_q_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16 *)m->qkv, stride, c.n_heads, c.head_dim, S, row0, base, m->cos_t, m->sin_t, pairs); break;
+    }
+    AB2_LAUNCH_CHECK();
+    return AB2_OK;
+}
+
+#define STEP(expr)                     \
+    do {                               \
+        int _rc = (expr);              \
+        if (_rc != AB2_OK) return _rc; \
+    } while (0)
+
+// The forward pass proper; every launch goes to `s`, nothing synchronises.
+static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S, int row0, int nrows,
+                            const int *rope_base, int logits_mode, void *logits, uint32_t *argmax_out,
+                            int len_hint, cudaStream_t s) {
+    const ab2_model_config &c = m->cfg;
+    const int T = nrows * S, d = c.d_model, hd = c.head_dim;
+    const size_t esz = dtype_size(m->dtype);
+    const long long qkv_stride = (long long)(c.n_heads + 2 * c.n_kv_heads) * hd;
+    const float scale = (float)(1.0 / std::sqrt((double)hd));
+    STEP(launch_embedding(m->embedding, ids, T, m->x, m->dtype, s));
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerWeights &L = m->layers[l];
+        STEP(launch_rms_norm(m->x, L.norm1, m->xn, T, d, c.rms_eps, m->dtype, s));
+        STEP(qlinear_dispatch(L.wqkv, m->xn, T, m->dtype, m->qkv, s));
+        STEP(launch_rope_q(m, T, S, row0, rope_base, s));
+        const char *kptr = (const char *)m->qkv + (size_t)c.n_heads * hd * esz;
+        const char *vptr = kptr + (size_t)c.n_kv_heads * hd * esz;
+        STEP(kv_append_device(kv, l, kptr, vptr, qkv_stride, S, row0, nrows, m->dtype, m->cos_t, m->sin_t,
+                              rope_base == kv->lens_dev ? nullptr : rope_base, s));
+        AttnStrides st;
+        st.q_h = hd; st.q_s = qkv_stride; st.q_b = qkv_stride * S;
+        st.o_h = hd; st.o_s = (long long)c.n_heads * hd; st.o_b = st.o_s * S;
+        STEP(attention_cached_device(kv, l, m->qkv, m->attn, S, S, row0, nrows, scale, m->dtype, st, len_hint, s));
+        STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
+        STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+        STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+        STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
+        STEP(launch_swiglu_fused(m->gu, m->hid, T, c.ffn_hidden, m->dtype, s));
+        STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
+        STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+    }
+    if (logits_mode == 0 && argmax_out == nullptr) return AB2_OK;
+    const void *hidden = m->x;
+    int rows = T;
+    if (logits_mode != 2 && S > 1) {  // only the last token of each row is needed
+        switch (m->dtype) {
+        case AB2_F32: gather_last_kernel<float><<<nrows, 128, 0, s>>>((const float *)m->x, (float *)m->proj, S, d); break;
+        case AB2_F16: gather_last_kernel<__half><<<nrows, 128, 0, s>>>((const __half *)m->x, (__half *)m->proj, S, d); break;
+        default: gather_last_kernel<__nv_bfloat16><<<nrows, 128, 0, s>>>((const __nv_bfloat16 *)m->x, (__nv_bfloat16 *)m->proj, S, d); break;
+        }
+        hidden = m->proj;
+        rows = nrows;
+    }
+    STEP(launch_rms_norm(hidden, m->final_norm, m->xn, rows, d, c.rms_eps, m->dtype, s));
+    void *lg = logits ? logits : m->gu;  // scratch when only the argmax is wanted
+    STEP(qlinear_dispatch(m->lm_head, m->xn, rows, m->dtype, lg, s));
+    if (argmax_out) {
+        // last token of each row
+        const char *src = (const char *)lg;
+        if (rows == T && S > 1) {
+            return fail(AB2_ERR_UNSUPPORTED, "argmax with all-token logits needs S == 1");
+        }
+        STEP(launch_argmax(src, nrows, c.vocab, m->dtype, argmax_out, s));
+    }
+    return AB2_OK;
+}
+
+static int check_forward(ab2_model *m, ab2_kv *kv, const void *ids, int S, int row0, int nrows,
+                         const int *offsets_host, int logits_mode, const void *logits) {
+    AB2_REQUIRE(m && kv && ids, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(m->finalized, AB2_ERR_BAD_ARG, "model is not finalised");
+    const ab2_model_config &c = m->cfg;
+    AB2_REQUIRE(kv->L == c.n_layers, AB2_ERR_BAD_SHAPE, "expected %d cache layers, got %d", c.n_layers, kv->L);
+    AB2_REQUIRE(kv->kvh == c.n_kv_heads && kv->hd == c.head_dim && kv->h == c.n_heads, AB2_ERR_BAD_SHAPE,
+                "KV cache head layout does not match the model");
+    AB2_REQUIRE(S > 0 && nrows > 0 && row0 >= 0 && row0 + nrows <= kv->B, AB2_ERR_BAD_SHAPE,
+                "rows %d..%d outside the cache batch %d", row0, row0 + nrows, kv->B);
+    AB2_REQUIRE(nrows * S <= m->max_tokens, AB2_ERR_CAPACITY, "%d tokens exceed the model workspace of %d", nrows * S, m->max_tokens);
+    AB2_REQUIRE(logits_mode >= 0 && logits_mode <= 2, AB2_ERR_BAD_ARG, "logits_mode must be 0, 1 or 2");
+    AB2_REQUIRE(logits_mode == 0 || logits != nullptr, AB2_ERR_BAD_ARG, "logits buffer is null");
+    for (int r = 0; r < nrows; ++r) {
+        int off = offsets_host ? offsets_host[r] : kv->lens_host[row0 + r];
+        AB2_REQUIRE(off >= 0 && off + S <= c.max_seq, AB2_ERR_BAD_SHAPE,
+                    "batch row %d offset %d exceeds max_seq_len %d", r, off, c.max_seq);
+        AB2_REQUIRE(kv->lens_host[row0 + r] + S <= kv->cap, AB2_ERR_CAPACITY, "KV cache length %d exceeds capacity %d",
+                    kv->lens_host[row0 + r] + S, kv->cap);
+    }
+    return AB2_OK;
+}
+
+}  // namespace ab2
+
+AB2_API int ab2_model_create(ab2_model **out, const ab2_model_config *cfg, ab2_dtype dtype, int max_tokens) {
+    AB2_REQUIRE(out && cfg, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(cfg->n_layers > 0 && cfg->d_model > 0 && cfg->n_heads > 0 && cfg->n_kv_heads > 0 &&
+                    cfg->head_dim > 0 && cfg->ffn_hidden > 0 && cfg->vocab > 0 && cfg->max_seq > 0,
+                AB2_ERR_BAD_SHAPE, "model dimensions must be positive");
+    AB2_REQUIRE(cfg->n_heads % cfg->n_kv_heads == 0, AB2_ERR_BAD_SHAPE, "n_heads must be a multiple of n_kv_heads");
+    AB2_REQUIRE(cfg->head_dim % 2 == 0, AB2_ERR_BAD_SHAPE, "head_dim must be even");
+    AB2_REQUIRE(dtype == AB2_F32 || dtype == AB2_F16 || dtype == AB2_BF16, AB2_ERR_BAD_DTYPE, "unsupported dtype %d", (int)dtype);
+    AB2_REQUIRE(max_tokens > 0, AB2_ERR_BAD_SHAPE, "max_tokens must be positive");
+    ab2_model *m = new ab2_model();
+    m->cfg = *cfg; m->dtype = dtype; m->max_tokens = max_tokens;
+    m->layers.resize(cfg->n_layers);
+    for (auto &L : m->layers) memset(&L, 0, sizeof(L));
+    m->embedding = m->lm_head = nullptr;
+    m->final_norm = m->cos_t = m->sin_t = nullptr;
+    m->finalized = false;
+    m->x = m->xn = m->qkv = m->attn = m->proj = m->gu = m->hid = nullptr;
+    m->positions = nullptr; m->positions_host = nullptr;
+    *out = m;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_destroy(ab2_model *m) {
+    if (!m) return AB2_OK;
+    for (auto &g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    for (auto &L : m->layers) {
+        ab2_qweight_destroy(L.wqkv); ab2_qweight_destroy(L.wgu);
+        cudaFree(L.norm1); cudaFree(L.norm2);
+    }
+    cudaFree(m->final_norm); cudaFree(m->cos_t); cudaFree(m->sin_t);
+    cudaFree(m->x); cudaFree(m->xn); cudaFree(m->qkv); cudaFree(m->attn); cudaFree(m->proj);
+    cudaFree(m->gu); cudaFree(m->hid); cudaFree(m->positions);
+    if (m->positions_host) cudaFreeHost(m->positions_host);
+    delete m;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_set_linear(ab2_model *m, int layer, int which, const ab2_qweight *w) {
+    AB2_REQUIRE(m && w, AB2_ERR_BAD_ARG, "null argument");
+    const ab2_model_config &c = m->cfg;
+    int N = 0, K = 0;
+    if (layer < 0) {
+        AB2_REQUIRE(which == 0 || which == 1, AB2_ERR_BAD_ARG, "model-level weight index must be 0 (embedding) or 1 (lm_head)");
+        N = c.vocab; K = c.d_model;
+    } else {
+        AB2_REQUIRE(layer < c.n_layers && which >= 0 && which < 7, AB2_ERR_BAD_ARG, "layer %d / weight %d out of range", layer, which);
+        const int qd = c.n_heads * c.head_dim, kd = c.n_kv_heads * c.head_dim;
+        const int Ns[7] = {qd, kd, kd, c.d_model, c.ffn_hidden, c.ffn_hidden, c.d_model};
+        const int Ks[7] = {c.d_model, c.d_model, c.d_model, qd, c.d_model, c.d_model, c.ffn_hidden};
+        N = Ns[which]; K = Ks[which];
+    }
+    AB2_REQUIRE(w->N == N && w->K == K, AB2_ERR_BAD_SHAPE, "weight is [%d,%d], expected [%d,%d]", w->N, w->K, N, K);
+    if (layer < 0) (which == 0 ? m->embedding : m->lm_head) = w;
+    else m->layers[layer].part[which] = w;
+    m->finalized = false;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_set_norm(ab2_model *m, int layer, int which, const float *weight) {
+    AB2_REQUIRE(m && weight, AB2_ERR_BAD_ARG, "null argument");
+    const int d = m->cfg.d_model;
+    float **slot;
+    if (layer < 0) slot = &m->final_norm;
+    else {
+        AB2_REQUIRE(layer < m->cfg.n_layers && (which == 0 || which == 1), AB2_ERR_BAD_ARG, "layer %d / norm %d out of range", layer, which);
+        slot = which == 0 ? &m->layers[layer].norm1 : &m->layers[layer].norm2;
+    }
+    if (!*slot) AB2_CUDA(cudaMalloc((void **)slot, (size_t)d * 4));
+    AB2_CUDA(cudaMemcpy(*slot, weight, (size_t)d * 4, cudaMemcpyDefault));
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_finalize(ab2_model *m) {
+    AB2_REQUIRE(m != nullptr, AB2_ERR_BAD_ARG, "null argument");
+    const ab2_model_config &c = m->cfg;
+    AB2_REQUIRE(m->embedding && m->final_norm, AB2_ERR_BAD_ARG, "embedding or final norm not set");
+    if (!m->lm_head) {
+        AB2_REQUIRE(c.tied, AB2_ERR_BAD_ARG, "lm_head not set and embeddings are not tied");
+        m->lm_head = m->embedding;  // LmHead::tied_with_qat (crates/aarambh-studio-model/src/head.rs:59-64)
+    }
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerWeights &L = m->layers[l];
+        for (int i = 0; i < 7; ++i) AB2_REQUIRE(L.part[i] != nullptr, AB2_ERR_BAD_ARG, "layer %d weight %d not set", l, i);
+        AB2_REQUIRE(L.norm1 && L.norm2, AB2_ERR_BAD_ARG, "layer %d norms not set", l);
+        ab2_qweight_destroy(L.wqkv); L.wqkv = nullptr;
+        ab2_qweight_destroy(L.wgu); L.wgu = nullptr;
+        const ab2_qweight *qkv[3] = {L.part[0], L.part[1], L.part[2]};
+        const ab2_qweight *gu[2] = {L.part[4], L.part[5]};
+        int rc = ab2_qweight_concat_rows(&L.wqkv, qkv, 3);
+        if (rc != AB2_OK) return rc;
+        rc = ab2_qweight_concat_rows(&L.wgu, gu, 2);
+        if (rc != AB2_OK) return rc;
+    }
+    // RoPE tables: inverse frequencies from an f64 pow cast to f32, angle in f32
+    // (crates/aarambh-studio-nn/src/rope_scaling.rs:6-11, rope.rs:54-64).
+    const int half = c.head_dim / 2;
+    std::vector<float> cosv((size_t)c.max_seq * half), sinv((size_t)c.max_seq * half);
+    for (int pos = 0; pos < c.max_seq; ++pos)
+        for (int i = 0; i < half; ++i) {
+            float inv = (float)(1.0 / std::pow(c.rope_theta, 2.0 * (double)i / (double)c.head_dim));
+            float val = (float)pos * inv;
+            cosv[(size_t)pos * half + i] = cosf(val);
+            sinv[(size_t)pos * half + i] = sinf(val);
+        }
+    if (!m->cos_t) {
+        AB2_CUDA(cudaMalloc((void **)&m->cos_t, cosv.size() * 4));
+        AB2_CUDA(cudaMalloc((void **)&m->sin_t, sinv.size() * 4));
+    }
+    AB2_CUDA(cudaMemcpy(m->cos_t, cosv.data(), cosv.size() * 4, cudaMemcpyHostToDevice));
+    AB2_CUDA(cudaMemcpy(m->sin_t, sinv.data(), sinv.size() * 4, cudaMemcpyHostToDevice));
+    if (!m->x) {
+        const size_t T = m->max_tokens, esz = dtype_size(m->dtype);
+        const size_t qkvw = (size_t)(c.n_heads + 2 * c.n_kv_heads) * c.head_dim;
+        const size_t guw = std::max((size_t)2 * c.ffn_hidden, (size_t)c.vocab);
+        AB2_CUDA(cudaMalloc(&m->x, T * c.d_model * esz));
+        AB2_CUDA(cudaMalloc(&m->xn, T * c.d_model * esz));
+        AB2_CUDA(cudaMalloc(&m->qkv, T * qkvw * esz));
+        AB2_CUDA(cudaMalloc(&m->attn, T * c.n_heads * c.head_dim * esz));
+        AB2_CUDA(cudaMalloc(&m->proj, T * c.d_model * esz));
+        AB2_CUDA(cudaMalloc(&m->gu, T * guw * esz));
+        AB2_CUDA(cudaMalloc(&m->hid, T * c.ffn_hidden * esz));
+        AB2_CUDA(cudaMalloc((void **)&m->positions, (size_t)m->max_tokens * 4));
+        AB2_CUDA(cudaMallocHost((void **)&m->positions_host, (size_t)m->max_tokens * 4));
+    }
+    for (auto &g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    m->graphs.clear();
+    int *status_word = nullptr;  // allocate the device status word outside any capture
+    int rc = device_status_word(&status_word);
+    if (rc != AB2_OK) return rc;
+    m->finalized = true;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_rope_tables(const ab2_model *m, const float **cos_dev, const float **sin_dev) {
+    AB2_REQUIRE(m && m->finalized, AB2_ERR_BAD_ARG, "model is not finalised");
+    if (cos_dev) *cos_dev = m->cos_t;
+    if (sin_dev) *sin_dev = m->sin_t;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, int row0, int nrows,
+                              const int *offsets_host, int logits_mode, void *logits_dev,
+                              uint32_t *argmax_dev, ab2_stream stream) {
+    int rc = check_forward(m, kv, ids_dev, S, row0, nrows, offsets_host, logits_mode, logits_dev);
+    if (rc != AB2_OK) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int *rope_base = kv->lens_dev;
+    if (offsets_host) {
+        bool same = true;
+        for (int r = 0; r < nrows; ++r) same = same && offsets_host[r] == kv->lens_host[row0 + r];
+        if (!same) {
+            // explicit seqlen offsets that differ from the cache lengths
+            AB2_CUDA(cudaStreamSynchronize(s));
+            for (int r = 0; r < nrows; ++r) m->positions_host[row0 + r] = offsets_host[r];
+            AB2_CUDA(cudaMemcpyAsync(m->positions + row0, m->positions_host + row0, (size_t)nrows * 4, cudaMemcpyHostToDevice, s));
+            rope_base = m->positions;
+        }
+    }
+    rc = forward_launches(m, kv, ids_dev, S, row0, nrows, rope_base, logits_mode, logits_dev, argmax_dev, 0, s);
+    if (rc != AB2_OK) return rc;
+    return kv_commit_device(kv, S, row0, nrows, s);
+}
+
+AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int row0, int nrows,
+                                  void *logits_dev, uint32_t *argmax_dev, ab2_stream stream) {
+    int rc = check_forward(m, kv, ids_dev, 1, row0, nrows, nullptr, logits_dev ? 1 : 0, logits_dev);
+    if (rc != AB2_OK) return rc;
+    AB2_REQUIRE(logits_dev || argmax_dev, AB2_ERR_BAD_ARG, "decode step needs a logits or an argmax output");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (s == nullptr || s == cudaStreamLegacy) {
+        // the legacy default stream cannot be captured: run the step as plain launches
+        rc = forward_launches(m, kv, ids_dev, 1, row0, nrows, kv->lens_dev, logits_dev ? 1 : 0, logits_dev, argmax_dev, 0, s);
+        if (rc != AB2_OK) return rc;
+        return kv_commit_device(kv, 1, row0, nrows, s);
+    }
+    auto key = std::make_tuple((const void *)kv, (const void *)ids_dev, row0, nrows, (const void *)logits_dev, (const void *)argmax_dev);
+    auto it = m->graphs.find(key);
+    if (it == m->graphs.end()) {
+        cudaGraph_t graph = nullptr;
+        AB2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        rc = forward_launches(m, kv, ids_dev, 1, row0, nrows, kv->lens_dev, logits_dev ? 1 : 0, logits_dev, argmax_dev, kv->cap, s);
+        if (rc == AB2_OK) {
+            // lengths advance inside the graph; the host mirror is advanced per replay
+            std::vector<int> keep(kv->lens_host, kv->lens_host + kv->B);
+            rc = kv_commit_device(kv, 1, row0, nrows, s);
+            memcpy(kv->lens_host, keep.data(), (size_t)kv->B * 4);
+        }
+        cudaError_t e = cudaStreamEndCapture(s, &graph);
+        if (rc != AB2_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        StepGraph sg;
+        e = cudaGraphInstantiate(&sg.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e));
+        it = m->graphs.emplace(key, sg).first;
+    }
+    AB2_CUDA(cudaGraphLaunch(it->second.exec, s));
+    for (int r = row0; r < row0 + nrows; ++r) kv->lens_host[r] += 1;
+    return AB2_OK;
+}

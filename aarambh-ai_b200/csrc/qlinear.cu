@@ -113,15 +113,18 @@ int qlinear_w4a16_mma(const ab2_qweight *w, const void *x, int M, void *y, cudaS
     return AB2_OK;
 }
 
+int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {
+    if (qlinear_w4a16_mma_eligible(w, dtype)) return qlinear_w4a16_mma(w, x, M, y, s);
+    return qlinear_generic(w, x, M, dtype, y, s);
+}
+
 }  // namespace ab2
 
 AB2_API int ab2_qlinear_forward(const ab2_qweight *w, const void *x_dev, int M, ab2_dtype dtype,
                                 void *y_dev, ab2_stream stream) {
     int rc = qlinear_validate(w, x_dev, M, dtype, y_dev);
     if (rc != AB2_OK) return rc;
-    if (qlinear_w4a16_mma_eligible(w, dtype))
-        return qlinear_w4a16_mma(w, x_dev, M, y_dev, (cudaStream_t)stream);
-    return qlinear_generic(w, x_dev, M, dtype, y_dev, (cudaStream_t)stream);
+    return qlinear_dispatch(w, x_dev, M, dtype, y_dev, (cudaStream_t)stream);
 }
 
 AB2_API int ab2_device_status(int *status_host) {

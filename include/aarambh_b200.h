@@ -115,6 +115,11 @@ int ab2_qweight_quantise_q4km(ab2_qweight **out, const float *w_dev, int N, int 
 int ab2_qweight_quantise_w4a16(ab2_qweight **out, const float *w_dev, int N, int K, int group,
                                ab2_stream stream);
 
+/* One packed weight holding the rows of `count` weights that share format,
+ * in_features and group size (Q|K|V and gate|up of a block, so that the three
+ * / two reference linears of crates/aarambh-studio-nn/src/attention.rs:182-184
+ * and ffn.rs:30-31 are one launch).  The parts stay valid and separate. */
+int ab2_qweight_concat_rows(ab2_qweight **out, const ab2_qweight *const *parts, int count);
 int ab2_qweight_destroy(ab2_qweight *w);
 int ab2_qweight_shape(const ab2_qweight *w, int *N, int *K, int *group, int *format);
 /* Bytes of packed storage held on the device (codes + parameters). */
@@ -134,6 +139,148 @@ int ab2_qweight_dequant(const ab2_qweight *w, void *out_dev, ab2_dtype dtype, ab
  * x and y have element type `dtype`; accumulation is f32. */
 int ab2_qlinear_forward(const ab2_qweight *w, const void *x_dev, int M, ab2_dtype dtype,
                         void *y_dev, ab2_stream stream);
+
+/* ---- element-wise operators of the decoder block ------------------------- */
+
+/* dispatch::rms_norm / RMSNorm::forward (crates/aarambh-studio-kernel/src/
+ * dispatch.rs:57-72, cpu/simd_norm.rs:51-57, kernels/rms_norm_fused.cu:56-84):
+ * out = x * (1 / sqrt(mean(x^2) + eps)) * weight over rows of length d.
+ * The weight is f32; x and out have element type `dtype`. */
+int ab2_rms_norm(const void *x_dev, const float *weight_dev, void *out_dev, int rows, int d, float eps,
+                 ab2_dtype dtype, ab2_stream stream);
+/* fused_rope_apply / RopeCache::apply_rotate (crates/aarambh-studio-kernel/src/
+ * fused_rope.rs:139-196, crates/aarambh-studio-nn/src/rope.rs:107-126):
+ * x [batch, seq, heads, head_dim]; half-split pairs (d, d + head_dim/2); token t
+ * uses table row offset + t.  Tables are f32 [max_seq, head_dim/2]. */
+int ab2_rope_apply(const void *x_dev, void *out_dev, const float *cos_dev, const float *sin_dev,
+                   int batch, int seq, int heads, int head_dim, int offset, int max_seq,
+                   ab2_dtype dtype, ab2_stream stream);
+/* fused_swiglu (crates/aarambh-studio-kernel/src/fused_ffn.rs:9-21,
+ * kernels/swiglu_fused.cu:43-54): out = gate / (1 + exp(-gate)) * up. */
+int ab2_swiglu(const void *gate_dev, const void *up_dev, void *out_dev, size_t n, ab2_dtype dtype,
+               ab2_stream stream);
+/* Greedy argmax of Sampler (crates/aarambh-studio-inference/src/sampler.rs:217-224)
+ * on the device: per row of logits [rows, vocab], the LAST index among equal
+ * maxima under the f32 total order.  Writes rows u32 indices. */
+int ab2_argmax(const void *logits_dev, int rows, int vocab, ab2_dtype dtype, uint32_t *out_dev,
+               ab2_stream stream);
+/* TokenEmbedding::forward (crates/aarambh-studio-model/src/embedding.rs:26-28) on a
+ * packed table (GGUF export quantises the embedding too, crates/
+ * aarambh-studio-weights/src/gguf.rs:133-150): out[t, :] = dequant(table[ids[t], :]). */
+int ab2_embedding_forward(const ab2_qweight *table, const uint32_t *ids_dev, int tokens, void *out_dev,
+                          ab2_dtype dtype, ab2_stream stream);
+
+/* ---- KV cache --------------------------------------------------------------
+ * KVCache with preallocated storage (crates/aarambh-studio-nn/src/kvcache.rs:
+ * 236-369) for `batch` independent sequences; INT8 storage quantises every
+ * (token, kv head) vector with the absmax arithmetic of
+ * crates/aarambh-studio-quant/src/absmax.rs:7-24 and f32 scales.  The reference's
+ * QuantisedKvCache (crates/aarambh-studio-quant/src/kv_quant.rs:16-74) uses one
+ * scale per tensor and re-quantises the whole cache on every append; this cache
+ * quantises each vector once.  n_heads is the number of query heads that will
+ * attend to it (sizes the split-context scratch). */
+int ab2_kv_create(ab2_kv **out, int n_layers, int batch, int capacity, int kv_heads, int head_dim,
+                  int n_heads, ab2_kv_dtype dtype);
+int ab2_kv_destroy(ab2_kv *kv);
+/* KVCache::update (kvcache.rs:335-368) for a single-layer cache: k, v
+ * [nrows, S, kv_heads, head_dim] of element type `dtype` are appended to rows
+ * row0..row0+nrows-1 at their current lengths, which then grow by S.
+ * AB2_ERR_CAPACITY when a row would exceed its capacity. */
+int ab2_kv_update(ab2_kv *kv, const void *k_dev, const void *v_dev, int S, int row0, int nrows,
+                  ab2_dtype dtype, ab2_stream stream);
+/* The two halves of update for the multi-layer cache the engine holds
+ * (KvCache, crates/aarambh-studio-inference/src/kvcache.rs:7-80: one length shared
+ * by all layers): ab2_kv_append writes layer `layer`'s S new tokens per row at
+ * the rows' current lengths without advancing them, optionally rotating K first
+ * (rope.apply_inference before update, crates/aarambh-studio-nn/src/attention.rs:
+ * 190-196,269-270; token s of a row uses table row positions_dev[row] + s, or its
+ * cache position when positions_dev is NULL; pass NULL tables for no rotation);
+ * ab2_kv_commit advances the rows' lengths by S once every layer has appended. */
+int ab2_kv_append(ab2_kv *kv, int layer, const void *k_dev, const void *v_dev, int S, int row0,
+                  int nrows, ab2_dtype dtype, const float *cos_dev, const float *sin_dev,
+                  const int *positions_dev, int max_seq, ab2_stream stream);
+int ab2_kv_commit(ab2_kv *kv, int S, int row0, int nrows, ab2_stream stream);
+/* KVCache::truncate (kvcache.rs:293-323): cannot grow (AB2_ERR_CAPACITY). */
+int ab2_kv_truncate(ab2_kv *kv, int row, int new_len, ab2_stream stream);
+/* KVCache::clear (kvcache.rs:284-290). */
+int ab2_kv_clear(ab2_kv *kv, ab2_stream stream);
+/* KVCache::seq_len / capacity (kvcache.rs:326-333). */
+int ab2_kv_seq_len(const ab2_kv *kv, int row, int *len);
+int ab2_kv_capacity(const ab2_kv *kv, int *capacity);
+/* KvCache::snapshot (crates/aarambh-studio-inference/src/kvcache.rs:57-64). */
+int ab2_kv_clone(ab2_kv **out, const ab2_kv *src, ab2_stream stream);
+/* The cached tensors KVCache::update returns, for one row, dequantised to f32
+ * in the reference layout [len, kv_heads, head_dim], for layer `layer`. */
+int ab2_kv_read(const ab2_kv *kv, int layer, int row, float *k_out_dev, float *v_out_dev,
+                ab2_stream stream);
+
+/* ---- attention --------------------------------------------------------------
+ * GroupedQueryAttention::forward_decode_batch attention step
+ * (crates/aarambh-studio-nn/src/attention.rs:265-283 -> dispatch::
+ * attention_forward_causal, crates/aarambh-studio-kernel/src/dispatch.rs:145-160):
+ * q, out [nrows, n_heads, head_dim]; one query per row over that row's cache
+ * (ragged lengths), query head j uses kv head j / (n_heads / kv_heads). */
+int ab2_attention_decode(const ab2_kv *kv, int layer, const void *q_dev, void *out_dev, int row0,
+                         int nrows, float scale, ab2_dtype dtype, ab2_stream stream);
+/* GroupedQueryAttention::forward attention step (attention.rs:170-226) for S new
+ * tokens per row that are already in the cache: q, out [nrows, S, n_heads,
+ * head_dim]; causal cut at len - S + query index
+ * (crates/aarambh-studio-kernel/src/cpu/parallel_attn.rs:205-209). */
+int ab2_attention_cached(const ab2_kv *kv, int layer, const void *q_dev, void *out_dev, int S, int row0,
+                         int nrows, float scale, ab2_dtype dtype, ab2_stream stream);
+/* dispatch::attention_forward_causal on explicit tensors (dispatch.rs:145-160):
+ * q, out [b, h, q_len, head_dim]; k, v [b, kv_heads, kv_len, head_dim] (the
+ * kv heads are NOT repeated).  Synchronises the stream. */
+int ab2_attention_causal(const void *q_dev, const void *k_dev, const void *v_dev, void *out_dev, int b,
+                         int h, int kv_heads, int q_len, int kv_len, int head_dim, float scale,
+                         ab2_dtype dtype, ab2_stream stream);
+
+/* ---- decoder -----------------------------------------------------------------
+ * The dense grouped-query decoder of AarambhModel (crates/aarambh-studio-model/
+ * src/model.rs) over packed weights.  Field names follow ModelConfig
+ * (crates/aarambh-studio-core/src/config.rs:734-868). */
+typedef struct {
+    int n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn_hidden, vocab, max_seq;
+    float rms_eps;      /* RMSNorm epsilon (1e-5) */
+    double rope_theta;  /* RoPE base (10000) */
+    int tied;           /* tied embeddings: lm_head shares the embedding weight */
+} ab2_model_config;
+
+/* `dtype` is the activation type of the whole model (the reference's model
+ * dtype); `max_tokens` bounds rows * S of one forward call (workspace size). */
+int ab2_model_create(ab2_model **out, const ab2_model_config *cfg, ab2_dtype dtype, int max_tokens);
+int ab2_model_destroy(ab2_model *m);
+/* Borrows a packed weight.  layer >= 0: which = 0 wq, 1 wk, 2 wv, 3 wo, 4 w_gate,
+ * 5 w_up, 6 w_down; layer < 0: which = 0 embedding, 1 lm_head. */
+int ab2_model_set_linear(ab2_model *m, int layer, int which, const ab2_qweight *w);
+/* Copies an f32 RMSNorm weight of d_model values (host or device).  layer >= 0:
+ * which = 0 norm1, 1 norm2; layer < 0: the final norm. */
+int ab2_model_set_norm(ab2_model *m, int layer, int which, const float *weight);
+/* Checks that every tensor is set, builds the fused projections, the RoPE
+ * tables (RopeCache::new, crates/aarambh-studio-nn/src/rope.rs:33-72) and the
+ * workspace. */
+int ab2_model_finalize(ab2_model *m);
+int ab2_model_rope_tables(const ab2_model *m, const float **cos_dev, const float **sin_dev);
+/* AarambhModel::forward_with_cache (model.rs:508-587; nrows = 1, S = prompt
+ * length) and forward_decode_batch (model.rs:590-641; S = 1): ids_dev
+ * [nrows, S] u32, rows row0..row0+nrows-1 of the cache.  offsets_host [nrows]
+ * are the seqlen offsets (RoPE positions); NULL uses the cache lengths.
+ * logits_mode 0: none; 1: last token of each row -> logits_dev [nrows, vocab];
+ * 2: every token -> [nrows, S, vocab] (element type = model dtype).
+ * argmax_dev (optional) receives the greedy token of each row's last position.
+ * Errors: AB2_ERR_BAD_SHAPE when offset + S exceeds max_seq (model.rs:609-615),
+ * AB2_ERR_CAPACITY when a cache row would overflow (kvcache.rs:337-342). */
+int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, int row0, int nrows,
+                      const int *offsets_host, int logits_mode, void *logits_dev, uint32_t *argmax_dev,
+                      ab2_stream stream);
+/* One decode step (S = 1, positions = cache lengths) replayed from a CUDA graph
+ * captured on first use for this (cache, ids buffer, rows, outputs)
+ * combination: InferenceEngine::decode_sessions
+ * (crates/aarambh-studio-inference/src/engine.rs:323-355) without the per-token
+ * host work.  ids_dev is read when the graph runs, so the previous step's
+ * argmax_dev may be passed as the next ids_dev. */
+int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int row0, int nrows,
+                          void *logits_dev, uint32_t *argmax_dev, ab2_stream stream);
 
 #ifdef __cplusplus
 }
