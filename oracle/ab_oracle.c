@@ -713,6 +713,25 @@ ORC_API int orc_model_truncate(orc_model *m, int b, int new_len) {
     return 0;
 }
 
+/* Test/benchmark helper (no reference counterpart): fills the first `len`
+ * positions of one sequence's caches in every layer with small pseudo-random
+ * values and sets its length, so that decode steps at a given context can be
+ * timed without running the prefill on the CPU. */
+ORC_API void orc_model_fill_cache(orc_model *m, int row, int len, uint32_t seed) {
+    size_t per_tok = (size_t)m->n_kv_heads * m->head_dim;
+    for (int l = 0; l < m->n_layers; ++l) {
+        uint32_t state = seed + 7919u * (uint32_t)l;
+        float *k = m->kc[l] + (size_t)row * m->cap * per_tok, *v = m->vc[l] + (size_t)row * m->cap * per_tok;
+        for (size_t i = 0; i < (size_t)len * per_tok; ++i) {
+            state = state * 1664525u + 1013904223u;
+            k[i] = ((float)(state >> 8) / 16777216.0f - 0.5f) * 2.0f;
+            state = state * 1664525u + 1013904223u;
+            v[i] = ((float)(state >> 8) / 16777216.0f - 0.5f) * 2.0f;
+        }
+    }
+    m->lens[row] = len;
+}
+
 ORC_API void orc_model_destroy(orc_model *m) {
     if (!m) return;
     for (int l = 0; l < m->n_layers; ++l) { free(m->kc[l]); free(m->vc[l]); }

@@ -91,6 +91,7 @@ def _declare(L):
     L.orc_model_truncate.argtypes = [C.c_void_p, C.c_int, C.c_int]
     L.orc_model_truncate.restype = C.c_int
     L.orc_model_destroy.argtypes = [C.c_void_p]
+    L.orc_model_fill_cache.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_uint32]
     L.orc_model_forward.argtypes = [C.c_void_p, _u32p, C.c_int, C.c_int, C.c_int, _i32p, _f32p]
     L.orc_model_forward.restype = C.c_int
 
@@ -427,6 +428,9 @@ class DenseModel:
         if rc != 0:
             raise ValueError("KV cache capacity or max_seq_len exceeded")
         return logits
+
+    def fill_cache(self, row, length, seed=1):
+        lib().orc_model_fill_cache(self.h, row, length, seed)
 
     def reset(self):
         lib().orc_model_reset(self.h)
