@@ -81,6 +81,7 @@ SIGNATURES = {
     "ab2_kv_clone": ([_pp, _p, _p], _i),
     "ab2_kv_read": ([_p, _i, _i, _p, _p, _p], _i),
     "ab2_attention_decode": ([_p, _i, _p, _p, _i, _i, _f, _i, _p], _i),
+    "ab2_attention_decode_static": ([_p, _i, _p, _p, _i, _i, _f, _i, _p], _i),
     "ab2_attention_cached": ([_p, _i, _p, _p, _i, _i, _i, _f, _i, _p], _i),
     "ab2_attention_causal": ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p], _i),
     "ab2_model_create": ([_pp, _p, _i, _i], _i),

@@ -364,6 +364,66 @@ AB2_API int ab2_attention_cached(const ab2_kv *kv, int layer, const void *q_dev,
     return attention_cached_device(kv, layer, q_dev, out_dev, S, 0, row0, nrows, scale, dtype, st, 0, (cudaStream_t)stream);
 }
 
+// ---------------------------------------------------------------------------
+// Decode attention for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc while they run: a serving
+// loop that has handed all free memory to its own pool, a caller holding a
+// lock the allocator would also need, or a process confined to a fixed memory
+// budget.  For them the partial results of the context splits live in the
+// fixed array below instead of in memory allocated with the cache.  Every GPU
+// that loads the library reserves the array until the process exits.
+// ---------------------------------------------------------------------------
+#define AB2_STATIC_SCRATCH_FLOATS (2u * 1024u * 1024u)  // 8 MiB
+static __device__ __align__(256) float g_static_attn_scratch[AB2_STATIC_SCRATCH_FLOATS];
+static float *g_static_attn_scratch_ptr[64] = {nullptr};
+
+AB2_API int ab2_attention_decode_static(const ab2_kv *kv, int layer, const void *q_dev, void *out_dev,
+                                        int row0, int nrows, float scale, ab2_dtype dtype,
+                                        ab2_stream stream) {
+    int rc = check_attention(kv, layer, q_dev, out_dev, 1, row0, nrows, dtype);
+    if (rc != AB2_OK) return rc;
+    AB2_REQUIRE(kv->hd == 64 || kv->hd == 128, AB2_ERR_UNSUPPORTED, "attention supports head_dim 64 and 128, got %d", kv->hd);
+    int dev = 0;
+    AB2_CUDA(cudaGetDevice(&dev));
+    AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
+    if (!g_static_attn_scratch_ptr[dev]) {
+        // Once per device, with that device current: the array's name is only a
+        // host-side stand-in, kernels need the address the runtime reports.
+        float *ptr = nullptr;
+        AB2_CUDA(cudaGetSymbolAddress((void **)&ptr, g_static_attn_scratch));
+        g_static_attn_scratch_ptr[dev] = ptr;
+    }
+    AttnArgs a;
+    a.kv = kv_view(kv, layer);
+    a.q = q_dev; a.out = out_dev; a.S = 1; a.pending = 0; a.row0 = row0; a.h = kv->h; a.rep = kv->h / kv->kvh;
+    a.dtype = (int)dtype; a.scale = scale;
+    a.st.q_b = (long long)kv->h * kv->hd; a.st.q_s = 0; a.st.q_h = kv->hd;
+    a.st.o_b = a.st.q_b; a.st.o_s = 0; a.st.o_h = kv->hd;
+    int max_len = 0;
+    for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r]);
+    const int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
+    a.nsplit = std::max(1, std::min(std::min(want, (max_len + 255) / 256), AB2_KV_MAX_SPLITS));
+    // Partials are indexed by the absolute row, exactly as in the allocated scratch.
+    const size_t parts = (size_t)(row0 + nrows) * kv->h * a.nsplit;
+    const size_t need = parts * ((size_t)kv->hd + 2);
+    AB2_REQUIRE(a.nsplit == 1 || need <= AB2_STATIC_SCRATCH_FLOATS, AB2_ERR_CAPACITY,
+                "decode attention needs %zu floats of split scratch (rows %d, heads %d, splits %d) but the "
+                "static scratch holds %u; use ab2_attention_decode",
+                need, row0 + nrows, kv->h, a.nsplit, (unsigned)AB2_STATIC_SCRATCH_FLOATS);
+    a.part_acc = g_static_attn_scratch_ptr[dev];
+    a.part_ml = g_static_attn_scratch_ptr[dev] + parts * kv->hd;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(a.nsplit, kv->kvh, nrows);
+    if (kv->dtype == AB2_KV_F32) rc = launch_split_hd<AB2_KV_F32>(a, grid, s);
+    else if (kv->dtype == AB2_KV_BF16) rc = launch_split_hd<AB2_KV_BF16>(a, grid, s);
+    else rc = launch_split_hd<AB2_KV_INT8>(a, grid, s);
+    if (rc != AB2_OK) return rc;
+    if (a.nsplit > 1) attn_merge_kernel<<<dim3(kv->h, nrows), kv->hd, 0, s>>>(a, kv->hd);
+    AB2_LAUNCH_CHECK();
+    return AB2_OK;
+}
+
 // dispatch::attention_forward_causal on explicit tensors: q [b,h,q_len,hd],
 // k,v [b,kv_heads,kv_len,hd] (not repeated), out [b,h,q_len,hd].
 AB2_API int ab2_attention_causal(const void *q_dev, const void *k_dev, const void *v_dev, void *out_dev,

@@ -84,6 +84,19 @@ def attention_decode(cache, q: torch.Tensor, scale: float, layer: int = 0, row0:
     return out
 
 
+def attention_decode_static(cache, q: torch.Tensor, scale: float, out: torch.Tensor, layer: int = 0,
+                            row0: int = 0) -> torch.Tensor:
+    """``attention_decode`` for hosts that must not allocate on the device: the
+    caller supplies ``out`` and the split scratch is a fixed array inside the
+    library (8 MiB; larger problems are rejected).  Calls on different streams
+    must not overlap."""
+    if not q.is_contiguous() or not out.is_contiguous() or out.shape != q.shape or out.dtype != q.dtype:
+        raise _lib.Ab2Error(-1, "q and out must be contiguous tensors of the same shape and dtype")
+    check(lib.ab2_attention_decode_static(cache._h, layer, q.data_ptr(), out.data_ptr(), row0, q.shape[0],
+                                          float(scale), dtype_code(q.dtype), stream_ptr()))
+    return out
+
+
 def attention_cached(cache, q: torch.Tensor, scale: float, layer: int = 0, row0: int = 0) -> torch.Tensor:
     """q [rows, S, n_heads, head_dim]: S new queries per sequence, causal."""
     q = _cuda(q, "q")

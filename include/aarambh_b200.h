@@ -222,6 +222,20 @@ int ab2_kv_read(const ab2_kv *kv, int layer, int row, float *k_out_dev, float *v
  * (ragged lengths), query head j uses kv head j / (n_heads / kv_heads). */
 int ab2_attention_decode(const ab2_kv *kv, int layer, const void *q_dev, void *out_dev, int row0,
                          int nrows, float scale, ab2_dtype dtype, ab2_stream stream);
+/* Same operation and result as ab2_attention_decode for callers that cannot
+ * allocate device memory (a serving loop whose memory pool owns all free HBM,
+ * a caller inside a lock the allocator needs, a fixed memory budget).  It has
+ * no counterpart in the reference.  It calls no cudaMalloc / cudaFree: the
+ * partial results of the context splits go to one fixed 8 MiB array inside the
+ * library, which every GPU that loads the library holds until the process
+ * exits.  Limit: (row0 + nrows) * n_heads * splits * (head_dim + 2) floats must
+ * fit in 2 Mi floats, otherwise AB2_ERR_CAPACITY (the message names the sizes).
+ * The first call on a device looks up the array's device address; make that
+ * first call before any stream capture.  All calls share the array: nothing in
+ * it needs clearing between calls (every slot a call reads it has written
+ * first), but two calls that overlap on the GPU (different streams) race. */
+int ab2_attention_decode_static(const ab2_kv *kv, int layer, const void *q_dev, void *out_dev, int row0,
+                                int nrows, float scale, ab2_dtype dtype, ab2_stream stream);
 /* GroupedQueryAttention::forward attention step (attention.rs:170-226) for S new
  * tokens per row that are already in the cache: q, out [nrows, S, n_heads,
  * head_dim]; causal cut at len - S + query index

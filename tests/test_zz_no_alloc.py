@@ -1,0 +1,60 @@
+"""The decode-attention entry point for callers that may not allocate device
+memory (its split scratch is a fixed array inside the library): it must return
+what the allocating entry point returns, on back-to-back calls that share the
+array, and refuse problems larger than the array.  Collected last on purpose."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import pkg
+
+pytestmark = pytest.mark.gpu
+
+
+def _cache(p, lens, h=32, kvh=8, hd=128, dtype="int8", seed=40):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    cache = p.KVCache(max(lens), kvh, hd, h, batch=len(lens), dtype=dtype)
+    for b, n in enumerate(lens):
+        k = torch.randn((1, n, kvh, hd), generator=gen, device="cuda")
+        v = torch.randn((1, n, kvh, hd), generator=gen, device="cuda")
+        cache.update(k, v, row0=b)
+    return cache
+
+
+@pytest.mark.parametrize("dtype,act", [("int8", torch.bfloat16), ("f32", torch.float32)])
+def test_static_scratch_entry_point_matches_allocating_one(dtype, act):
+    p = pkg()
+    lens = [3000, 700]
+    cache = _cache(p, lens, dtype=dtype)
+    gen = torch.Generator(device="cuda").manual_seed(41)
+    scale = 1 / math.sqrt(128)
+    qs = [torch.randn((2, 32, 128), generator=gen, device="cuda").to(act) for _ in range(2)]
+    want = [p.dispatch.attention_decode(cache, q, scale) for q in qs]
+    outs = [torch.empty_like(q) for q in qs]
+    # two calls in a row on one stream: the second reuses the scratch the first left behind
+    for q, o in zip(qs, outs):
+        p.dispatch.attention_decode_static(cache, q, scale, o)
+    torch.cuda.synchronize()
+    for w, o in zip(want, outs):
+        assert torch.isfinite(o.float()).all()
+        err = (o.float() - w.float()).abs().max().item() / w.float().abs().max().item()
+        assert err < 1e-6, err
+    assert p.device_status() == 0
+
+
+def test_static_scratch_rejects_oversized_problems():
+    p = pkg()
+    # Partials are indexed by the absolute cache row: rows 78..79 of an 80-row cache
+    # with 19 context splits need 80 * 32 * 19 * 130 = 6.3 M floats, more than the
+    # 2 Mi floats of the fixed array; rows 0..1 need 2 * 32 * 19 * 130 = 158 k.
+    lens = [5000, 5000] + [8] * 76 + [5000, 5000]
+    cache = _cache(p, lens, seed=42)
+    q = torch.randn((2, 32, 128), device="cuda").to(torch.bfloat16)
+    with pytest.raises(p.Ab2Error) as e:
+        p.dispatch.attention_decode_static(cache, q, 0.1, torch.empty_like(q), row0=78)
+    assert e.value.status == -4 and "static scratch" in str(e.value)
+    ok = p.dispatch.attention_decode_static(cache, q, 0.1, torch.empty_like(q), row0=0)
+    want = p.dispatch.attention_decode(cache, q, 0.1, row0=0)
+    assert torch.equal(ok, want)
