@@ -58,6 +58,7 @@ SIGNATURES = {
     "ab2_qweight_quantise_q4km": ([_pp, _p, _i, _i, _p], _i),
     "ab2_qweight_quantise_w4a16": ([_pp, _p, _i, _i, _i, _p], _i),
     "ab2_qweight_concat_rows": ([_pp, _pp, _i], _i),
+    "ab2_qweight_interleave_gate_up": ([_pp, _p, _p], _i),
     "ab2_qweight_destroy": ([_p], _i),
     "ab2_qweight_shape": ([_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)], _i),
     "ab2_qweight_nbytes": ([_p, C.POINTER(C.c_size_t)], _i),

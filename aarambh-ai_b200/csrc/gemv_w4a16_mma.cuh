@@ -25,6 +25,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "ops.cuh"
 #include "w4a16_layout.cuh"
 
 namespace ab2 {
@@ -124,10 +125,18 @@ constexpr int W4_STAGE_WORDS = W4_GROUPS_PER_STAGE * W4_BLOCK_WORDS;
 // stores the outputs, so there is no CTA-wide barrier in the steady state and
 // the result does not depend on arrival order.  Two partial buffers suffice
 // because a warp can run at most `stages` <= chunks items ahead of another.
-template <int NT>
+//
+// EPI selects what the reducing warp stores: the projection (W4_EPI_STORE), the
+// residual plus the projection (W4_EPI_ADD; `resid` may alias `y`), or
+// silu(gate) * up for a weight whose 16-row tiles hold 8 gate rows followed by
+// the 8 matching up rows (W4_EPI_SWIGLU; y is [M][N/2]).
+enum { W4_EPI_STORE = 0, W4_EPI_ADD = 1, W4_EPI_SWIGLU = 2 };
+
+template <int NT, int EPI>
 __global__ void __launch_bounds__(256)
 gemv_w4a16_stream_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__restrict__ x,
-                         __nv_bfloat16 *__restrict__ y, int N, int K, int M, int *status) {
+                         __nv_bfloat16 *y, const __nv_bfloat16 *resid, int N, int K, int M,
+                         int *status) {
     constexpr int MAX_STAGES = NT == 1 ? 4 : 3;  // keeps static shared memory under 48 KB
     __shared__ alignas(128) uint32_t ring[MAX_STAGES][W4_STAGE_WORDS];
     __shared__ float red[2][8][16][8 * NT + 1];
@@ -304,11 +313,26 @@ gemv_w4a16_stream_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *_
             const int row0 = tile * 16;
             for (int idx = lane; idx < 16 * 8 * NT; idx += 32) {
                 const int tok = idx >> 4, row = idx & 15;
-                if (tok < M && row0 + row < N) {
+                if (EPI == W4_EPI_SWIGLU) {
+                    // rows 0..7 of the tile are gate rows, rows 8..15 the matching up rows
+                    const int half_n = N >> 1, col = tile * 8 + row;
+                    if (row < 8 && tok < M && col < half_n) {
+                        float g = 0.f, u = 0.f;
+#pragma unroll
+                        for (int w = 0; w < 8; ++w) { g += red[buf][w][row][tok]; u += red[buf][w][row + 8][tok]; }
+                        // the reference rounds gate and up to the activation type first
+                        g = __bfloat162float(__float2bfloat16_rn(g));
+                        u = __bfloat162float(__float2bfloat16_rn(u));
+                        y[(size_t)tok * half_n + col] = __float2bfloat16_rn(swiglu_value(g, u));
+                    }
+                } else if (tok < M && row0 + row < N) {
                     float v = 0.f;
 #pragma unroll
                     for (int w = 0; w < 8; ++w) v += red[buf][w][row][tok];
-                    y[(size_t)tok * N + row0 + row] = __float2bfloat16_rn(v);
+                    const size_t o = (size_t)tok * N + row0 + row;
+                    if (EPI == W4_EPI_ADD)  // residual + bf16(projection), as residual + x does
+                        v = __bfloat162float(resid[o]) + __bfloat162float(__float2bfloat16_rn(v));
+                    y[o] = __float2bfloat16_rn(v);
                 }
             }
             __syncwarp();

@@ -20,7 +20,11 @@ using namespace ab2;
 namespace ab2 {
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s);
 int device_status_word(int **out);
+bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype);
+int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s);
+int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 }
+extern "C" int ab2_qweight_interleave_gate_up(ab2_qweight **out, const ab2_qweight *gate, const ab2_qweight *up);
 
 struct LayerWeights {
     const ab2_qweight *part[7];  // wq wk wv wo gate up down (borrowed)
@@ -41,6 +45,7 @@ struct ab2_model {
     float *final_norm;
     float *cos_t, *sin_t;  // [max_seq][head_dim/2]
     bool finalized;
+    bool fused_epilogues;  // W4A16 + bf16: residual add and SwiGLU ride the GEMV epilogues
     // workspace, sized for max_tokens
     void *x, *xn, *qkv, *attn, *proj, *gu, *hid;
     int *positions;        // [max rows] explicit RoPE offsets
@@ -121,13 +126,20 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         st.q_h = hd; st.q_s = qkv_stride; st.q_b = qkv_stride * S;
         st.o_h = hd; st.o_s = (long long)c.n_heads * hd; st.o_b = st.o_s * S;
         STEP(attention_cached_device(kv, l, m->qkv, m->attn, S, S, row0, nrows, scale, m->dtype, st, len_hint, s));
-        STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
-        STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
-        STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
-        STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
-        STEP(launch_swiglu_fused(m->gu, m->hid, T, c.ffn_hidden, m->dtype, s));
-        STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
-        STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+        if (m->fused_epilogues) {
+            STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
+            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+            STEP(qlinear_w4a16_mma_swiglu(L.wgu, m->xn, T, m->hid, s));
+            STEP(qlinear_w4a16_mma_add(L.part[6], m->hid, T, m->x, m->x, s));
+        } else {
+            STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
+            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+            STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
+            STEP(launch_swiglu_fused(m->gu, m->hid, T, c.ffn_hidden, m->dtype, s));
+            STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
+            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+        }
     }
     if (logits_mode == 0 && argmax_out == nullptr) return AB2_OK;
     const void *hidden = m->x;
@@ -260,6 +272,11 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
         AB2_REQUIRE(c.tied, AB2_ERR_BAD_ARG, "lm_head not set and embeddings are not tied");
         m->lm_head = m->embedding;  // LmHead::tied_with_qat (crates/aarambh-studio-model/src/head.rs:59-64)
     }
+    bool fast = true;
+    for (int l = 0; l < c.n_layers && fast; ++l)
+        for (int i = 0; i < 7; ++i)
+            fast = fast && m->layers[l].part[i] && qlinear_w4a16_mma_eligible(m->layers[l].part[i], m->dtype);
+    m->fused_epilogues = fast && c.ffn_hidden % 8 == 0;
     for (int l = 0; l < c.n_layers; ++l) {
         LayerWeights &L = m->layers[l];
         for (int i = 0; i < 7; ++i) AB2_REQUIRE(L.part[i] != nullptr, AB2_ERR_BAD_ARG, "layer %d weight %d not set", l, i);
@@ -270,7 +287,8 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
         const ab2_qweight *gu[2] = {L.part[4], L.part[5]};
         int rc = ab2_qweight_concat_rows(&L.wqkv, qkv, 3);
         if (rc != AB2_OK) return rc;
-        rc = ab2_qweight_concat_rows(&L.wgu, gu, 2);
+        rc = m->fused_epilogues ? ab2_qweight_interleave_gate_up(&L.wgu, gu[0], gu[1])
+                                : ab2_qweight_concat_rows(&L.wgu, gu, 2);
         if (rc != AB2_OK) return rc;
     }
     // RoPE tables: inverse frequencies from an f64 pow cast to f32, angle in f32

@@ -95,22 +95,38 @@ bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype) {
     return w->fmt == FMT_W4A16 && w->group == 128 && dtype == AB2_BF16;
 }
 
-int qlinear_w4a16_mma(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+template <int EPI>
+static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void *y, const void *resid,
+                               cudaStream_t s) {
     int *status = nullptr;
     int rc = device_status_word(&status);
     if (rc != AB2_OK) return rc;
     const int tiles = (w->N + 15) / 16;
     const int grid = std::min(tiles, device_sm_count() * 4);
     const uint32_t *wt = (const uint32_t *)w->codes;
+    const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     for (int m0 = 0; m0 < M; m0 += 16) {
         const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;
-        __nv_bfloat16 *yp = (__nv_bfloat16 *)y + (size_t)m0 * w->N;
+        __nv_bfloat16 *yp = (__nv_bfloat16 *)y + (size_t)m0 * out_n;
+        const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
         int mv = M - m0 < 16 ? M - m0 : 16;
-        if (mv <= 8) gemv_w4a16_stream_kernel<1><<<grid, 256, 0, s>>>(wt, xp, yp, w->N, w->K, mv, status);
-        else gemv_w4a16_stream_kernel<2><<<grid, 256, 0, s>>>(wt, xp, yp, w->N, w->K, mv, status);
+        if (mv <= 8) gemv_w4a16_stream_kernel<1, EPI><<<grid, 256, 0, s>>>(wt, xp, yp, rp, w->N, w->K, mv, status);
+        else gemv_w4a16_stream_kernel<2, EPI><<<grid, 256, 0, s>>>(wt, xp, yp, rp, w->N, w->K, mv, status);
     }
     AB2_LAUNCH_CHECK();
     return AB2_OK;
+}
+
+int qlinear_w4a16_mma(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+    return launch_w4a16_stream<W4_EPI_STORE>(w, x, M, y, nullptr, s);
+}
+// y = resid + x . W^T (resid may be y)
+int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s) {
+    return launch_w4a16_stream<W4_EPI_ADD>(w, x, M, y, resid, s);
+}
+// y[M][N/2] = silu(gate) * up for a gate|up weight interleaved in 8-row halves
+int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+    return launch_w4a16_stream<W4_EPI_SWIGLU>(w, x, M, y, nullptr, s);
 }
 
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {

@@ -92,3 +92,51 @@ AB2_API int ab2_qweight_concat_rows(ab2_qweight **out, const ab2_qweight *const 
     *out = w;
     return AB2_OK;
 }
+
+// gate|up of a SwiGLU block as one W4A16 weight whose 16-row tiles hold 8 gate
+// rows followed by the 8 matching up rows, so the GEMV epilogue can form
+// silu(gate) * up without writing the two projections out
+// (crates/aarambh-studio-nn/src/ffn.rs:29-37).
+__global__ void w4a16_interleave8_kernel(const uint32_t *gate, const uint32_t *up, W4Layout src,
+                                         W4Layout dst, uint32_t *out) {
+    // one thread per destination word of the code and parameter planes
+    const int wpr = dst.words_per_row(), G = dst.G();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t per_row = (size_t)G * (wpr + 1);
+    if (i >= (size_t)dst.N * per_row) return;
+    int n = (int)(i / per_row), rest = (int)(i % per_row);
+    int g = rest / (wpr + 1), j = rest % (wpr + 1);
+    int tile = n >> 4, r = n & 15;
+    int src_row = tile * 8 + (r & 7);
+    const uint32_t *from = (r < 8) ? gate : up;
+    if (src_row >= src.N) return;  // padded rows stay zero
+    if (j < wpr) out[dst.code_index(n, g * wpr + j)] = from[src.code_index(src_row, g * wpr + j)];
+    else out[dst.param_index(n, g)] = from[src.param_index(src_row, g)];
+}
+
+AB2_API int ab2_qweight_interleave_gate_up(ab2_qweight **out, const ab2_qweight *gate, const ab2_qweight *up) {
+    AB2_REQUIRE(out && gate && up, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(gate->fmt == FMT_W4A16 && up->fmt == FMT_W4A16, AB2_ERR_UNSUPPORTED, "interleaving is defined for W4A16 weights");
+    AB2_REQUIRE(gate->N == up->N && gate->K == up->K && gate->group == up->group, AB2_ERR_BAD_SHAPE, "gate and up must have the same shape and group size");
+    AB2_REQUIRE(gate->N % 8 == 0, AB2_ERR_BAD_SHAPE, "out_features must be a multiple of 8, got %d", gate->N);
+    ab2_qweight *w = new ab2_qweight();
+    memset(w, 0, sizeof(*w));
+    w->fmt = FMT_W4A16; w->N = 2 * gate->N; w->K = gate->K; w->group = gate->group;
+    cudaGetDevice(&w->device);
+    W4Layout src{gate->N, gate->K, gate->group}, dst{w->N, w->K, w->group};
+    w->codes_bytes = (size_t)dst.tiles() * 16 * w->K / 2;
+    w->param_bytes = (size_t)dst.tiles() * 16 * dst.G() * 4;
+    cudaError_t e = cudaMalloc(&w->codes, dst.total_words() * 4);
+    if (e == cudaSuccess) e = cudaMemset(w->codes, 0, dst.total_words() * 4);
+    if (e == cudaSuccess) {
+        size_t n = (size_t)dst.N * dst.G() * (dst.words_per_row() + 1);
+        w4a16_interleave8_kernel<<<(unsigned)ceil_div(n, 256), 256>>>((const uint32_t *)gate->codes, (const uint32_t *)up->codes, src, dst, (uint32_t *)w->codes);
+        e = cudaDeviceSynchronize();
+    }
+    if (e != cudaSuccess) {
+        ab2_qweight_destroy(w);
+        return fail(AB2_ERR_CUDA, "interleaving failed: %s", cudaGetErrorString(e));
+    }
+    *out = w;
+    return AB2_OK;
+}

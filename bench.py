@@ -202,6 +202,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--cpu-steps", type=int, default=12)
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     args = ap.parse_args()
 
     import torch
@@ -329,7 +330,7 @@ def main():
         "clocks": clocks.summary(),
         "device_status": status,
     }
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.skip_cpu:
         tok_s, cores, dt = cpu_decode_baseline(pkg, torch, weights, cfg, args.cpu_steps, 2, PROMPT)
         line["cpu_baseline"] = {"value": round(tok_s, 4), "unit": "tokens/s", "cores": cores, "kind": "port",
                                 "sample": f"{args.cpu_steps} decode steps at batch 1, context {PROMPT} (cache pre-filled), all 32 layers"}

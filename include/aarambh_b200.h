@@ -120,6 +120,10 @@ int ab2_qweight_quantise_w4a16(ab2_qweight **out, const float *w_dev, int N, int
  * / two reference linears of crates/aarambh-studio-nn/src/attention.rs:182-184
  * and ffn.rs:30-31 are one launch).  The parts stay valid and separate. */
 int ab2_qweight_concat_rows(ab2_qweight **out, const ab2_qweight *const *parts, int count);
+/* gate|up of SwiGluFfn (crates/aarambh-studio-nn/src/ffn.rs:29-37) as one W4A16
+ * weight of 2 * ffn rows whose every 16 rows are 8 gate rows followed by the 8
+ * matching up rows: the layout the decoder's fused projection + SwiGLU uses. */
+int ab2_qweight_interleave_gate_up(ab2_qweight **out, const ab2_qweight *gate, const ab2_qweight *up);
 int ab2_qweight_destroy(ab2_qweight *w);
 int ab2_qweight_shape(const ab2_qweight *w, int *N, int *K, int *group, int *format);
 /* Bytes of packed storage held on the device (codes + parameters). */

@@ -106,3 +106,34 @@ def test_bf16_int8kv_model_close_to_oracle():
     lg = gpu.forward_with_cache(ids[None], 0, cache).float().cpu().numpy()
     ref = cpu.forward(ids[None], [0])
     assert rel_err(lg, ref) < 2e-2
+
+
+def test_fused_epilogue_path_matches_unfused_operators():
+    """Large-class block shapes scaled down: the decoder's fused projection
+    epilogues (residual add, SwiGLU) against the same step assembled from the
+    unfused operators of the C ABI."""
+    import math
+    p = pkg()
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=1)
+    gpu, _, packed = build_pair(cfg, "w4a16", dtype=torch.bfloat16, capacity=32)
+    ids = torch.tensor([[5, 9, 200, 17]])
+    cache = gpu.empty_kv_cache_with_capacity(32, dtype="bf16")
+    got = gpu.forward_with_cache(ids, 0, cache).float()
+    D = p.dispatch
+    bf = torch.bfloat16
+    x = D.embedding_forward(packed["embedding"], ids.cuda(), bf)[0]
+    cos, sin = [torch.from_numpy(a).cuda() for a in orc.rope_tables(cfg["max_seq"], 128)]
+    ones = torch.ones(512, device="cuda")
+    xn = D.rms_norm(x, ones, 1e-5)
+    q = packed["layers.0.wq"](xn).view(1, 4, 4, 128); k = packed["layers.0.wk"](xn).view(1, 4, 2, 128)
+    v = packed["layers.0.wv"](xn).view(1, 4, 2, 128)
+    q = D.fused_rope_apply(q, cos, sin, 0); k = D.fused_rope_apply(k, cos, sin, 0)
+    c2 = p.KVCache(32, 2, 128, 4, dtype="bf16")
+    c2.update(k, v)
+    att = D.attention_cached(c2, q, 1 / math.sqrt(128)).view(4, 512)
+    x = x + packed["layers.0.wo"](att)
+    xn = D.rms_norm(x, ones, 1e-5)
+    hid = D.fused_swiglu(packed["layers.0.w_gate"](xn), packed["layers.0.w_up"](xn))
+    x = x + packed["layers.0.w_down"](hid)
+    ref = packed["embedding"](D.rms_norm(x, ones, 1e-5)).float()
+    assert rel_err(got[0].cpu().numpy(), ref.cpu().numpy()) < 1e-2
