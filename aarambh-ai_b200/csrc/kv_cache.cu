@@ -197,6 +197,8 @@ AB2_API int ab2_kv_create(ab2_kv **out, int n_layers, int batch, int capacity, i
     size_t nparts = (size_t)batch * n_heads * kv->max_splits;
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->part_acc, nparts * head_dim * 4);
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->part_ml, nparts * 2 * 4);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->counters, (size_t)batch * kv_heads * 4);
+    if (e == cudaSuccess) e = cudaMemset(kv->counters, 0, (size_t)batch * kv_heads * 4);
     if (e != cudaSuccess) {
         ab2_kv_destroy(kv);
         return fail(AB2_ERR_CUDA, "KV cache allocation failed: %s", cudaGetErrorString(e));
@@ -209,7 +211,7 @@ AB2_API int ab2_kv_create(ab2_kv **out, int n_layers, int batch, int capacity, i
 AB2_API int ab2_kv_destroy(ab2_kv *kv) {
     if (!kv) return AB2_OK;
     cudaFree(kv->k); cudaFree(kv->v); cudaFree(kv->ks); cudaFree(kv->vs); cudaFree(kv->lens_dev);
-    cudaFree(kv->part_acc); cudaFree(kv->part_ml);
+    cudaFree(kv->part_acc); cudaFree(kv->part_ml); cudaFree(kv->counters);
     if (kv->lens_host) cudaFreeHost(kv->lens_host);
     delete kv;
     return AB2_OK;

@@ -16,6 +16,7 @@ struct ab2_kv {
     float *part_acc;  // [B][h][max_splits][hd]
     float *part_ml;   // [B][h][max_splits][2]  (running max, running sum)
     int max_splits;
+    int *counters;    // [B][kvh] split-arrival counters of the fused decode attention (zero at rest)
 };
 
 namespace ab2 {
@@ -48,5 +49,9 @@ struct AttnStrides {
 int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *out, int S, int pending,
                             int row0, int nrows, float scale, ab2_dtype dtype, AttnStrides st,
                             int len_hint, cudaStream_t s);
+
+int attention_decode_fused_device(ab2_kv *kv, int layer, const void *qkv, long long stride, void *out,
+                                  int row0, int nrows, float scale, ab2_dtype dtype, const float *cos_t,
+                                  const float *sin_t, const int *rope_pos, int len_hint, cudaStream_t s);
 
 }  // namespace ab2

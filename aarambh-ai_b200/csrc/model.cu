@@ -117,15 +117,22 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         LayerWeights &L = m->layers[l];
         STEP(launch_rms_norm(m->x, L.norm1, m->xn, T, d, c.rms_eps, m->dtype, s));
         STEP(qlinear_dispatch(L.wqkv, m->xn, T, m->dtype, m->qkv, s));
-        STEP(launch_rope_q(m, T, S, row0, rope_base, s));
-        const char *kptr = (const char *)m->qkv + (size_t)c.n_heads * hd * esz;
-        const char *vptr = kptr + (size_t)c.n_kv_heads * hd * esz;
-        STEP(kv_append_device(kv, l, kptr, vptr, qkv_stride, S, row0, nrows, m->dtype, m->cos_t, m->sin_t,
-                              rope_base == kv->lens_dev ? nullptr : rope_base, s));
-        AttnStrides st;
-        st.q_h = hd; st.q_s = qkv_stride; st.q_b = qkv_stride * S;
-        st.o_h = hd; st.o_s = (long long)c.n_heads * hd; st.o_b = st.o_s * S;
-        STEP(attention_cached_device(kv, l, m->qkv, m->attn, S, S, row0, nrows, scale, m->dtype, st, len_hint, s));
+        if (S == 1) {
+            // decode: RoPE, KV append, attention and split merge in one launch
+            STEP(attention_decode_fused_device(kv, l, m->qkv, qkv_stride, m->attn, row0, nrows, scale, m->dtype,
+                                               m->cos_t, m->sin_t, rope_base == kv->lens_dev ? nullptr : rope_base,
+                                               len_hint, s));
+        } else {
+            STEP(launch_rope_q(m, T, S, row0, rope_base, s));
+            const char *kptr = (const char *)m->qkv + (size_t)c.n_heads * hd * esz;
+            const char *vptr = kptr + (size_t)c.n_kv_heads * hd * esz;
+            STEP(kv_append_device(kv, l, kptr, vptr, qkv_stride, S, row0, nrows, m->dtype, m->cos_t, m->sin_t,
+                                  rope_base == kv->lens_dev ? nullptr : rope_base, s));
+            AttnStrides st;
+            st.q_h = hd; st.q_s = qkv_stride; st.q_b = qkv_stride * S;
+            st.o_h = hd; st.o_s = (long long)c.n_heads * hd; st.o_b = st.o_s * S;
+            STEP(attention_cached_device(kv, l, m->qkv, m->attn, S, S, row0, nrows, scale, m->dtype, st, len_hint, s));
+        }
         if (m->fused_epilogues) {
             STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
             STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));

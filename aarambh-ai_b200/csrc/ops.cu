@@ -1,6 +1,7 @@
 // Element-wise operators of the decoder block: RMSNorm, RoPE, SwiGLU, residual
 // add, embedding gather and greedy argmax.  These are the unfused forms behind
 // the C ABI; the decoder step uses the same device functions.
+#include <algorithm>
 #include <cfloat>
 
 #include "common.cuh"
@@ -41,8 +42,68 @@ __global__ void rms_norm_kernel(const T *__restrict__ x, const float *__restrict
         out[(size_t)blockIdx.x * d + i] = from_f32<T>(__fmul_rn(__fmul_rn(to_f32(row[i]), inv), w[i]));
 }
 
+// bf16 rows with d % 8 == 0: every thread owns 8-element vectors, all loads of a
+// row are in flight at once (decode rows are latency-bound, not bandwidth-bound).
+__global__ void rms_norm_bf16_vec_kernel(const __nv_bfloat16 *__restrict__ x, const float *__restrict__ w,
+                                         __nv_bfloat16 *out, int d, float eps) {
+    __shared__ float warp_sums[32];
+    __shared__ float inv_shared;
+    const uint4 *row = reinterpret_cast<const uint4 *>(x + (size_t)blockIdx.x * d);
+    const int nvec = d >> 3;
+    uint4 v[2];
+    float sum = 0.f;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        v[it] = i < nvec ? row[i] : make_uint4(0, 0, 0, 0);
+        const uint32_t r[4] = {v[it].x, v[it].y, v[it].z, v[it].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a = __uint_as_float(r[j] << 16), b = __uint_as_float(r[j] & 0xffff0000u);
+            sum = fmaf(a, a, sum);
+            sum = fmaf(b, b, sum);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? warp_sums[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) inv_shared = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)d), eps)));
+    }
+    __syncthreads();
+    const float inv = inv_shared;
+    uint4 *orow = reinterpret_cast<uint4 *>(out + (size_t)blockIdx.x * d);
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i >= nvec) continue;
+        const float4 w0 = reinterpret_cast<const float4 *>(w)[2 * i], w1 = reinterpret_cast<const float4 *>(w)[2 * i + 1];
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const uint32_t r[4] = {v[it].x, v[it].y, v[it].z, v[it].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a = __uint_as_float(r[j] << 16), b = __uint_as_float(r[j] & 0xffff0000u);
+            const __nv_bfloat16 oa = __float2bfloat16_rn(__fmul_rn(__fmul_rn(a, inv), ww[2 * j]));
+            const __nv_bfloat16 ob = __float2bfloat16_rn(__fmul_rn(__fmul_rn(b, inv), ww[2 * j + 1]));
+            o[j] = (uint32_t)__bfloat16_as_ushort(oa) | ((uint32_t)__bfloat16_as_ushort(ob) << 16);
+        }
+        orow[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 int launch_rms_norm(const void *x, const float *w, void *out, int rows, int d, float eps,
                     ab2_dtype dtype, cudaStream_t s) {
+    if (dtype == AB2_BF16 && d % 8 == 0 && d / 8 <= 2048 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0) {
+        int threads = std::min(1024, ((d / 8 + 1) / 2 + 31) / 32 * 32);
+        rms_norm_bf16_vec_kernel<<<rows, threads, 0, s>>>((const __nv_bfloat16 *)x, w, (__nv_bfloat16 *)out, d, eps);
+        AB2_LAUNCH_CHECK();
+        return AB2_OK;
+    }
     int threads = d >= 1024 ? 256 : 128;
     switch (dtype) {
     case AB2_F32: rms_norm_kernel<float><<<rows, threads, 0, s>>>((const float *)x, w, (float *)out, d, eps); break;
