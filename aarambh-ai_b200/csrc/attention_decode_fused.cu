@@ -119,6 +119,38 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
     const int t0 = split * per, t1 = min(pos, t0 + per);
     const size_t tok_base = (size_t)rrow * a.stride;
     const float *cs = a.cos_t + (size_t)rpos * half, *sn = a.sin_t + (size_t)rpos * half;
+    const size_t head_base = ((size_t)row * a.kv.kvh + kvhead) * a.kv.cap;
+
+    // The cached K/V of older tokens do not depend on the preceding kernel: the
+    // raw bytes of this warp's first chunk are requested before waiting for it,
+    // all at once, so the chunk costs one memory round trip instead of a chain.
+    constexpr bool STAGED = (KVD != AB2_KV_F32) && HD == 128;
+    constexpr int ESZ = KVD == AB2_KV_INT8 ? 1 : 2;
+    constexpr int KW = STAGED ? HD * ESZ / 16 : 1;  // 16-byte words of one K row
+    constexpr int VW = STAGED ? DPL * ESZ / 4 : 1;  // 4-byte words of one lane's V slice
+    uint4 kraw[KW];
+    uint32_t vraw[32][VW];
+    float kscale_c = 1.f, vscale_c = 1.f;
+    auto stage_chunk = [&](int base) {
+        const int tok = min(base + lane, t1 - 1);
+        const size_t trow = head_base + tok;
+        const uint4 *kp = reinterpret_cast<const uint4 *>((const char *)a.kv.k + trow * HD * ESZ);
+#pragma unroll
+        for (int i = 0; i < KW; ++i) kraw[i] = kp[i];
+        if (KVD == AB2_KV_INT8) { kscale_c = a.kv.ks[trow]; vscale_c = a.kv.vs[trow]; }
+        const int last = t1 - 1 - base;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            const uint32_t *vp = reinterpret_cast<const uint32_t *>(
+                (const char *)a.kv.v + ((head_base + base + min(t, last)) * HD + lane * DPL) * ESZ);
+#pragma unroll
+            for (int i = 0; i < VW; ++i) vraw[t][i] = vp[i];
+        }
+    };
+    const int first_base = t0 + warp * 32;
+    if (STAGED && first_base < t1) stage_chunk(first_base);
+    pdl_wait();  // q, k, v of the new token come from the preceding projection
+    pdl_launch_dependents();
 
     // ---- Q: rotate, round to the activation type
     for (int i = tid; i < REP * half; i += 128) {
@@ -189,7 +221,6 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
         __syncthreads();
     }
 
-    const size_t head_base = ((size_t)row * a.kv.kvh + kvhead) * a.kv.cap;
     float m_run[REP], l_run[REP], acc[REP][DPL];
 #pragma unroll
     for (int hh = 0; hh < REP; ++hh) {
@@ -204,13 +235,37 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
         const int tok = base + lane;
         const bool valid = tok < t1;
         const size_t trow = head_base + (valid ? tok : t1 - 1);
+        if (STAGED && base != first_base) stage_chunk(base);
         float sc[REP];
 #pragma unroll
         for (int hh = 0; hh < REP; ++hh) sc[hh] = 0.f;
 #pragma unroll
         for (int d0 = 0; d0 < HD; d0 += 16) {
             float kf[16];
-            ld_kv<KVD, 16>(a.kv.k, trow * HD + d0, kf);
+            if constexpr (STAGED) {
+                if constexpr (KVD == AB2_KV_INT8) {
+                    const uint32_t w4[4] = {kraw[d0 / 16].x, kraw[d0 / 16].y, kraw[d0 / 16].z, kraw[d0 / 16].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float t[4];
+                        i8x4(w4[i], t);
+                        kf[4 * i] = t[0]; kf[4 * i + 1] = t[1]; kf[4 * i + 2] = t[2]; kf[4 * i + 3] = t[3];
+                    }
+                } else {
+#pragma unroll
+                    for (int hv = 0; hv < 2; ++hv) {
+                        const uint4 r4 = kraw[d0 / 8 + hv];
+                        const uint32_t w4[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            kf[8 * hv + 2 * i] = __uint_as_float(w4[i] << 16);
+                            kf[8 * hv + 2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+                        }
+                    }
+                }
+            } else {
+                ld_kv<KVD, 16>(a.kv.k, trow * HD + d0, kf);
+            }
 #pragma unroll
             for (int hh = 0; hh < REP; ++hh) {
 #pragma unroll
@@ -223,8 +278,8 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
                 }
             }
         }
-        float kscale = 1.f, vscale = 1.f;
-        if (KVD == AB2_KV_INT8) { kscale = a.kv.ks[trow]; vscale = a.kv.vs[trow]; }
+        float kscale = kscale_c, vscale = vscale_c;
+        if (!STAGED && KVD == AB2_KV_INT8) { kscale = a.kv.ks[trow]; vscale = a.kv.vs[trow]; }
 #pragma unroll
         for (int hh = 0; hh < REP; ++hh) {
             const float s = valid ? sc[hh] * kscale * a.scale : -INFINITY;
@@ -244,23 +299,42 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
             ps[warp][hh][lane] = p * vscale;
         }
         __syncwarp();
-        // PV: every load of a batch is issued before its FMAs; rows past the end
-        // are read from the last valid row and weighted by p = 0.
-        const int last = t1 - 1 - base;
+        // PV: lanes span head_dim; rows past the end were staged from the last valid
+        // row and are weighted by p = 0.
+        if constexpr (STAGED) {
 #pragma unroll
-        for (int tb = 0; tb < 32; tb += VUNROLL) {
-            float vf[VUNROLL][DPL];
-#pragma unroll
-            for (int t = 0; t < VUNROLL; ++t)
-                ld_kv<KVD, DPL>(a.kv.v, (head_base + base + min(tb + t, last)) * HD + lane * DPL, vf[t]);
-#pragma unroll
-            for (int t = 0; t < VUNROLL; ++t)
+            for (int t = 0; t < 32; ++t) {
+                float vf[DPL];
+                if constexpr (KVD == AB2_KV_INT8) {
+                    i8x4(vraw[t][0], vf);
+                } else {
+                    vf[0] = __uint_as_float(vraw[t][0] << 16); vf[1] = __uint_as_float(vraw[t][0] & 0xffff0000u);
+                    vf[2] = __uint_as_float(vraw[t][1] << 16); vf[3] = __uint_as_float(vraw[t][1] & 0xffff0000u);
+                }
 #pragma unroll
                 for (int hh = 0; hh < REP; ++hh) {
-                    const float p = ps[warp][hh][tb + t];
+                    const float p = ps[warp][hh][t];
 #pragma unroll
-                    for (int j = 0; j < DPL; ++j) acc[hh][j] = fmaf(p, vf[t][j], acc[hh][j]);
+                    for (int j = 0; j < DPL; ++j) acc[hh][j] = fmaf(p, vf[j], acc[hh][j]);
                 }
+            }
+        } else {
+            const int last = t1 - 1 - base;
+#pragma unroll
+            for (int tb = 0; tb < 32; tb += VUNROLL) {
+                float vf[VUNROLL][DPL];
+#pragma unroll
+                for (int t = 0; t < VUNROLL; ++t)
+                    ld_kv<KVD, DPL>(a.kv.v, (head_base + base + min(tb + t, last)) * HD + lane * DPL, vf[t]);
+#pragma unroll
+                for (int t = 0; t < VUNROLL; ++t)
+#pragma unroll
+                    for (int hh = 0; hh < REP; ++hh) {
+                        const float p = ps[warp][hh][tb + t];
+#pragma unroll
+                        for (int j = 0; j < DPL; ++j) acc[hh][j] = fmaf(p, vf[t][j], acc[hh][j]);
+                    }
+            }
         }
         __syncwarp();
     }
@@ -343,10 +417,10 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
 
 template <int KVD, int HD>
 void launch_fused(const FusedArgs &a, dim3 grid, cudaStream_t s) {
-    if (a.rep == 1) attn_decode_fused_kernel<KVD, HD, 1><<<grid, 128, 0, s>>>(a);
-    else if (a.rep == 2) attn_decode_fused_kernel<KVD, HD, 2><<<grid, 128, 0, s>>>(a);
-    else if (a.rep <= 4) attn_decode_fused_kernel<KVD, HD, 4><<<grid, 128, 0, s>>>(a);
-    else attn_decode_fused_kernel<KVD, HD, 8><<<grid, 128, 0, s>>>(a);
+    if (a.rep == 1) launch_kernel(attn_decode_fused_kernel<KVD, HD, 1>, grid, dim3(128), 0, s, a);
+    else if (a.rep == 2) launch_kernel(attn_decode_fused_kernel<KVD, HD, 2>, grid, dim3(128), 0, s, a);
+    else if (a.rep <= 4) launch_kernel(attn_decode_fused_kernel<KVD, HD, 4>, grid, dim3(128), 0, s, a);
+    else launch_kernel(attn_decode_fused_kernel<KVD, HD, 8>, grid, dim3(128), 0, s, a);
 }
 
 template <int KVD>

@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 #include <string>
 
@@ -88,5 +89,35 @@ __device__ __forceinline__ float f16_bits_to_f32(uint16_t b) {
 }
 
 static inline size_t dtype_size(ab2_dtype d) { return d == AB2_F32 ? 4 : 2; }
+
+// ---- programmatic dependent launch ------------------------------------------
+// Kernels of the decoder step are launched so that a kernel may start while its
+// predecessor is still draining: everything that does not depend on the
+// predecessor (barrier set-up, the first bulk copies of the constant weights)
+// runs ahead of pdl_wait(), which returns once the predecessor grid has
+// completed and its writes are visible.  Every kernel of the chain calls
+// pdl_wait() before it finishes, so completion stays transitive.  Without the
+// launch attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+
+// Set by the decoder step around its launches.
+extern thread_local bool g_pdl_launch;
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t s, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool force = getenv("AB2_FORCE_PDL") != nullptr;  // experiments: chain every launch
+    cfg.numAttrs = (g_pdl_launch || force) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace ab2

@@ -180,6 +180,11 @@ gemv_w4a16_stream_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *_
     if (producer)
         for (int j = 0; j < min(stages, items); ++j) issue_next();
 
+    // The weights are constant, so their first stages are already in flight; the
+    // activations (and the residual) come from the preceding kernel.
+    pdl_wait();
+    pdl_launch_dependents();
+
     // Opaque register copies of the two constants of the nibble extraction.
     uint32_t k_mask = 0x000F000Fu, k_magic = 0x43004300u;
     asm volatile("" : "+r"(k_mask), "+r"(k_magic));

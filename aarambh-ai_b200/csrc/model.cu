@@ -385,6 +385,7 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
     if (it == m->graphs.end()) {
         cudaGraph_t graph = nullptr;
         AB2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        g_pdl_launch = m->fused_epilogues;  // every kernel of the fast path takes part in the chain
         rc = forward_launches(m, kv, ids_dev, 1, row0, nrows, kv->lens_dev, logits_dev ? 1 : 0, logits_dev, argmax_dev, kv->cap, s);
         if (rc == AB2_OK) {
             // lengths advance inside the graph; the host mirror is advanced per replay
@@ -392,6 +393,7 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
             rc = kv_commit_device(kv, 1, row0, nrows, s);
             memcpy(kv->lens_host, keep.data(), (size_t)kv->B * 4);
         }
+        g_pdl_launch = false;
         cudaError_t e = cudaStreamEndCapture(s, &graph);
         if (rc != AB2_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
         if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));

@@ -48,6 +48,8 @@ __global__ void rms_norm_bf16_vec_kernel(const __nv_bfloat16 *__restrict__ x, co
                                          __nv_bfloat16 *out, int d, float eps) {
     __shared__ float warp_sums[32];
     __shared__ float inv_shared;
+    pdl_wait();
+    pdl_launch_dependents();
     const uint4 *row = reinterpret_cast<const uint4 *>(x + (size_t)blockIdx.x * d);
     const int nvec = d >> 3;
     uint4 v[2];
@@ -100,8 +102,9 @@ int launch_rms_norm(const void *x, const float *w, void *out, int rows, int d, f
                     ab2_dtype dtype, cudaStream_t s) {
     if (dtype == AB2_BF16 && d % 8 == 0 && d / 8 <= 2048 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0) {
         int threads = std::min(1024, ((d / 8 + 1) / 2 + 31) / 32 * 32);
-        rms_norm_bf16_vec_kernel<<<rows, threads, 0, s>>>((const __nv_bfloat16 *)x, w, (__nv_bfloat16 *)out, d, eps);
-        AB2_LAUNCH_CHECK();
+        cudaError_t e = launch_kernel(rms_norm_bf16_vec_kernel, dim3(rows), dim3(threads), 0, s,
+                                      (const __nv_bfloat16 *)x, w, (__nv_bfloat16 *)out, d, eps);
+        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "RMSNorm launch failed: %s", cudaGetErrorString(e));
         return AB2_OK;
     }
     int threads = d >= 1024 ? 256 : 128;

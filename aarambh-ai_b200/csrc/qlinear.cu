@@ -67,6 +67,8 @@ int qlinear_generic(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype,
     }
 }
 
+thread_local bool g_pdl_launch = false;
+
 // Per-device status word written by kernels whose bounded waits ran out.
 static int *g_status_word[64] = {nullptr};
 static int g_sm_count[64] = {0};
@@ -110,8 +112,10 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
         __nv_bfloat16 *yp = (__nv_bfloat16 *)y + (size_t)m0 * out_n;
         const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
         int mv = M - m0 < 16 ? M - m0 : 16;
-        if (mv <= 8) gemv_w4a16_stream_kernel<1, EPI><<<grid, 256, 0, s>>>(wt, xp, yp, rp, w->N, w->K, mv, status);
-        else gemv_w4a16_stream_kernel<2, EPI><<<grid, 256, 0, s>>>(wt, xp, yp, rp, w->N, w->K, mv, status);
+        cudaError_t e;
+        if (mv <= 8) e = launch_kernel(gemv_w4a16_stream_kernel<1, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
+        else e = launch_kernel(gemv_w4a16_stream_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
+        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "GEMV launch failed: %s", cudaGetErrorString(e));
     }
     AB2_LAUNCH_CHECK();
     return AB2_OK;
