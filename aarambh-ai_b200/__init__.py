@@ -8,3 +8,5 @@ from .qlinear import QuantLinear  # noqa: F401
 from .kvcache import KVCache  # noqa: F401
 from . import dispatch  # noqa: F401
 from .model import AarambhModel, InferenceEngine, ModelConfig  # noqa: F401
+from . import parallel  # noqa: F401
+from .parallel import TensorParallel  # noqa: F401

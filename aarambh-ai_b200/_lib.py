@@ -90,6 +90,11 @@ SIGNATURES = {
     "ab2_model_set_linear": ([_p, _i, _i, _p], _i),
     "ab2_model_set_norm": ([_p, _i, _i, _p], _i),
     "ab2_model_finalize": ([_p], _i),
+    "ab2_model_set_tp": ([_p, _p], _i),
+    "ab2_tp_unique_id": ([_p], _i),
+    "ab2_tp_create": ([_pp, _i, _i, _p], _i),
+    "ab2_tp_destroy": ([_p], _i),
+    "ab2_tp_all_reduce": ([_p, _p, C.c_size_t, _i, _p], _i),
     "ab2_model_rope_tables": ([_p, _pp, _pp], _i),
     "ab2_model_forward": ([_p, _p, _p, _i, _i, _i, _p, _i, _p, _p, _p], _i),
     "ab2_model_decode_step": ([_p, _p, _p, _i, _i, _p, _p, _p], _i),

@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "kv_cache.cuh"
 #include "ops.cuh"
+#include "tp.cuh"
 
 using namespace ab2;
 
@@ -46,6 +47,8 @@ struct ab2_model {
     float *cos_t, *sin_t;  // [max_seq][head_dim/2]
     bool finalized;
     bool fused_epilogues;  // W4A16 + bf16: residual add and SwiGLU ride the GEMV epilogues
+    ab2_tp *tp;            // tensor-parallel context (borrowed), or null
+    void *lg_local, *lg_all;  // tensor-parallel logits: this rank's vocabulary shard / all shards
     // workspace, sized for max_tokens
     void *x, *xn, *qkv, *attn, *proj, *gu, *hid;
     int *positions;        // [max rows] explicit RoPE offsets
@@ -81,6 +84,18 @@ template <typename T>
 __global__ void gather_last_kernel(const T *in, T *out, int S, int d) {
     const T *src = in + ((size_t)blockIdx.x * S + (S - 1)) * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)blockIdx.x * d + i] = src[i];
+}
+
+// [world][rows][vn] (all-gathered vocabulary shards) -> [rows][world * vn]
+template <typename T>
+__global__ void reorder_shards_kernel(const T *in, T *out, int rows, int vn, int world) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t n = (size_t)rows * vn * world;
+    if (i >= n) return;
+    int j = (int)(i % vn);
+    int r = (int)((i / vn) % world);
+    int b = (int)(i / ((size_t)vn * world));
+    out[i] = in[((size_t)r * rows + b) * vn + j];
 }
 
 static int launch_rope_q(ab2_model *m, int T, int S, int row0, const int *base, cudaStream_t s) {
@@ -133,7 +148,23 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             st.o_h = hd; st.o_s = (long long)c.n_heads * hd; st.o_b = st.o_s * S;
             STEP(attention_cached_device(kv, l, m->qkv, m->attn, S, S, row0, nrows, scale, m->dtype, st, len_hint, s));
         }
-        if (m->fused_epilogues) {
+        const bool tp = m->tp && m->tp->world > 1;
+        if (tp) {
+            // row-parallel O and down produce partial sums: all-reduce, then the residual add
+            STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
+            STEP(tp_all_reduce(m->tp, m->proj, (size_t)T * d, m->dtype, s));
+            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+            if (m->fused_epilogues) {
+                STEP(qlinear_w4a16_mma_swiglu(L.wgu, m->xn, T, m->hid, s));
+            } else {
+                STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
+                STEP(launch_swiglu_fused(m->gu, m->hid, T, c.ffn_hidden, m->dtype, s));
+            }
+            STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
+            STEP(tp_all_reduce(m->tp, m->proj, (size_t)T * d, m->dtype, s));
+            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+        } else if (m->fused_epilogues) {
             STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
             STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
             STEP(qlinear_w4a16_mma_swiglu(L.wgu, m->xn, T, m->hid, s));
@@ -162,7 +193,22 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
     }
     STEP(launch_rms_norm(hidden, m->final_norm, m->xn, rows, d, c.rms_eps, m->dtype, s));
     void *lg = logits ? logits : m->gu;  // scratch when only the argmax is wanted
-    STEP(qlinear_dispatch(m->lm_head, m->xn, rows, m->dtype, lg, s));
+    if (m->tp && m->tp->world > 1) {
+        // vocabulary-parallel LM head: local shard, all-gather, reorder to [rows][vocab]
+        const int vn = c.vocab / m->tp->world;
+        STEP(qlinear_dispatch(m->lm_head, m->xn, rows, m->dtype, m->lg_local, s));
+        void *gathered = rows == 1 ? lg : m->lg_all;
+        STEP(tp_all_gather(m->tp, m->lg_local, gathered, (size_t)rows * vn, m->dtype, s));
+        if (rows > 1) {
+            size_t n = (size_t)rows * c.vocab;
+            unsigned blocks = (unsigned)ceil_div(n, 256);
+            if (esz == 4) reorder_shards_kernel<float><<<blocks, 256, 0, s>>>((const float *)m->lg_all, (float *)lg, rows, vn, m->tp->world);
+            else reorder_shards_kernel<uint16_t><<<blocks, 256, 0, s>>>((const uint16_t *)m->lg_all, (uint16_t *)lg, rows, vn, m->tp->world);
+            AB2_LAUNCH_CHECK();
+        }
+    } else {
+        STEP(qlinear_dispatch(m->lm_head, m->xn, rows, m->dtype, lg, s));
+    }
     if (argmax_out) {
         // last token of each row
         const char *src = (const char *)lg;
@@ -217,6 +263,7 @@ AB2_API int ab2_model_create(ab2_model **out, const ab2_model_config *cfg, ab2_d
     m->finalized = false;
     m->x = m->xn = m->qkv = m->attn = m->proj = m->gu = m->hid = nullptr;
     m->positions = nullptr; m->positions_host = nullptr;
+    m->tp = nullptr; m->lg_local = m->lg_all = nullptr; m->fused_epilogues = false;
     *out = m;
     return AB2_OK;
 }
@@ -230,7 +277,7 @@ AB2_API int ab2_model_destroy(ab2_model *m) {
     }
     cudaFree(m->final_norm); cudaFree(m->cos_t); cudaFree(m->sin_t);
     cudaFree(m->x); cudaFree(m->xn); cudaFree(m->qkv); cudaFree(m->attn); cudaFree(m->proj);
-    cudaFree(m->gu); cudaFree(m->hid); cudaFree(m->positions);
+    cudaFree(m->gu); cudaFree(m->hid); cudaFree(m->positions); cudaFree(m->lg_local); cudaFree(m->lg_all);
     if (m->positions_host) cudaFreeHost(m->positions_host);
     delete m;
     return AB2_OK;
@@ -242,7 +289,8 @@ AB2_API int ab2_model_set_linear(ab2_model *m, int layer, int which, const ab2_q
     int N = 0, K = 0;
     if (layer < 0) {
         AB2_REQUIRE(which == 0 || which == 1, AB2_ERR_BAD_ARG, "model-level weight index must be 0 (embedding) or 1 (lm_head)");
-        N = c.vocab; K = c.d_model;
+        N = (which == 1 && m->tp) ? c.vocab / m->tp->world : c.vocab;
+        K = c.d_model;
     } else {
         AB2_REQUIRE(layer < c.n_layers && which >= 0 && which < 7, AB2_ERR_BAD_ARG, "layer %d / weight %d out of range", layer, which);
         const int qd = c.n_heads * c.head_dim, kd = c.n_kv_heads * c.head_dim;
@@ -326,6 +374,10 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
         AB2_CUDA(cudaMalloc(&m->proj, T * c.d_model * esz));
         AB2_CUDA(cudaMalloc(&m->gu, T * guw * esz));
         AB2_CUDA(cudaMalloc(&m->hid, T * c.ffn_hidden * esz));
+        if (m->tp && m->tp->world > 1) {
+            AB2_CUDA(cudaMalloc(&m->lg_local, T * (c.vocab / m->tp->world) * esz));
+            AB2_CUDA(cudaMalloc(&m->lg_all, T * c.vocab * esz));
+        }
         AB2_CUDA(cudaMalloc((void **)&m->positions, (size_t)m->max_tokens * 4));
         AB2_CUDA(cudaMallocHost((void **)&m->positions_host, (size_t)m->max_tokens * 4));
     }
@@ -335,6 +387,14 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
     int rc = device_status_word(&status_word);
     if (rc != AB2_OK) return rc;
     m->finalized = true;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_set_tp(ab2_model *m, ab2_tp *tp) {
+    AB2_REQUIRE(m != nullptr, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(m->x == nullptr, AB2_ERR_BAD_ARG, "set the tensor-parallel context before the model is finalised");
+    if (tp) AB2_REQUIRE(m->cfg.vocab % tp->world == 0, AB2_ERR_BAD_SHAPE, "vocab %d is not divisible by the world size %d", m->cfg.vocab, tp->world);
+    m->tp = tp;
     return AB2_OK;
 }
 

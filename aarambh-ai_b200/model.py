@@ -50,14 +50,18 @@ class AarambhModel:
     ``final_norm`` and ``layers.{i}.{norm1,norm2}``."""
 
     def __init__(self, cfg: ModelConfig, weights: dict, dtype: torch.dtype = torch.float32,
-                 max_tokens: int = 512):
-        self.cfg, self.dtype, self.weights = cfg, dtype, weights
+                 max_tokens: int = 512, tp=None):
+        """With ``tp`` (a ``parallel.TensorParallel``), ``cfg`` and ``weights`` are
+        this rank's shard (``parallel.shard_config`` / ``shard_weight``)."""
+        self.cfg, self.dtype, self.weights, self.tp = cfg, dtype, weights, tp
         c = _CConfig(cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn_hidden,
                      cfg.vocab_size, cfg.max_seq_len, cfg.rms_norm_eps, cfg.rope_theta,
                      1 if cfg.tie_embeddings else 0)
         h = C.c_void_p()
         check(lib.ab2_model_create(C.byref(h), C.byref(c), dtype_code(dtype), max_tokens))
         self._h = h
+        if tp is not None:
+            check(lib.ab2_model_set_tp(self._h, tp._h))
         check(lib.ab2_model_set_linear(self._h, -1, 0, weights["embedding"]._h))
         if "lm_head" in weights:
             check(lib.ab2_model_set_linear(self._h, -1, 1, weights["lm_head"]._h))

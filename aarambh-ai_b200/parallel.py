@@ -1,0 +1,106 @@
+"""Tensor-parallel sharding of the decoder over the GPUs of one box.
+
+One process per GPU.  ``TensorParallel`` wraps the library's NCCL communicator
+(``ab2_tp_*``); the 128-byte unique id travels through ``torch.distributed``
+(plumbing only).  The ``shard_*`` helpers are pure tensor slicing and define
+which part of every weight a rank owns:
+
+* column parallel (wq, wk, wv, w_gate, w_up, lm_head): a contiguous block of
+  output rows of the ``[out, in]`` weight — whole heads for the attention
+  projections, so the KV cache and the attention of a rank are local;
+* row parallel (wo, w_down): a contiguous block of input columns, a multiple
+  of the quantisation group so no group straddles two ranks; the partial
+  outputs are summed by an all-reduce.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import replace
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+COLUMN_PARALLEL = ("wq", "wk", "wv", "w_gate", "w_up", "lm_head")
+ROW_PARALLEL = ("wo", "w_down")
+
+
+def shard_config(cfg, world: int):
+    """The ModelConfig a rank builds its model with (local heads and FFN width)."""
+    if cfg.n_heads % world or cfg.n_kv_heads % world or cfg.ffn_hidden % world or cfg.vocab_size % world:
+        raise _lib.Ab2Error(-1, f"heads {cfg.n_heads}/{cfg.n_kv_heads}, ffn {cfg.ffn_hidden} and vocab "
+                                f"{cfg.vocab_size} must be divisible by the world size {world}")
+    return replace(cfg, n_heads=cfg.n_heads // world, n_kv_heads=cfg.n_kv_heads // world,
+                   ffn_hidden=cfg.ffn_hidden // world)
+
+
+def shard_rows(weight: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Column-parallel shard: rows [rank * N/world, (rank + 1) * N/world) of [N, K]."""
+    n = weight.shape[0]
+    if n % world:
+        raise _lib.Ab2Error(-1, f"{n} output rows are not divisible by {world}")
+    step = n // world
+    return weight[rank * step:(rank + 1) * step].contiguous()
+
+
+def shard_cols(weight: torch.Tensor, rank: int, world: int, group: int = 128) -> torch.Tensor:
+    """Row-parallel shard: input columns [rank * K/world, (rank + 1) * K/world) of [N, K]."""
+    k = weight.shape[1]
+    if k % world or (k // world) % group:
+        raise _lib.Ab2Error(-1, f"{k} input columns do not split into {world} multiples of the group size {group}")
+    step = k // world
+    return weight[:, rank * step:(rank + 1) * step].contiguous()
+
+
+def shard_weight(name: str, weight: torch.Tensor, rank: int, world: int, group: int = 128) -> torch.Tensor:
+    """The part of tensor ``name`` (e.g. ``layers.3.wo``) that ``rank`` owns."""
+    leaf = name.split(".")[-1]
+    if world == 1 or weight.dim() != 2:
+        return weight
+    if leaf in COLUMN_PARALLEL:
+        return shard_rows(weight, rank, world)
+    if leaf in ROW_PARALLEL:
+        return shard_cols(weight, rank, world, group)
+    return weight  # embedding and norms are replicated
+
+
+class TensorParallel:
+    """The NCCL communicator of this process inside the library."""
+
+    def __init__(self, rank: int, world: int, unique_id: bytes | None):
+        self.rank, self.world = rank, world
+        h = C.c_void_p()
+        buf = C.create_string_buffer(unique_id, 128) if unique_id is not None else None
+        check(lib.ab2_tp_create(C.byref(h), rank, world, buf))
+        self._h = h
+
+    @staticmethod
+    def new_unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        check(lib.ab2_tp_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def from_torch_distributed(cls):
+        """Rank 0 makes the id; it is broadcast over the default process group."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        if world == 1:
+            return cls(0, 1, None)
+        ids = [cls.new_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        return cls(rank, world, ids[0])
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        from .qlinear import dtype_code, stream_ptr
+        check(lib.ab2_tp_all_reduce(self._h, t.data_ptr(), t.numel(), dtype_code(t.dtype), stream_ptr()))
+        return t
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib.ab2_tp_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass

@@ -108,24 +108,27 @@ class ClockSampler:
 
 
 def build_large(pkg, torch, cfg, seed=0, tp_rank=0, tp_world=1):
-    """Random N(0, 0.02) weights, quantised on the GPU to group-128 INT4."""
+    """Random N(0, 0.02) weights, quantised on the GPU to group-128 INT4.  Under
+    tensor parallelism every rank draws the same full weights and keeps its shard."""
     gen = torch.Generator(device="cuda").manual_seed(seed)
     weights = {}
 
-    def make(n, k):
+    def make(name, n, k):
         w = torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02
-        return pkg.QuantLinear.quantise(w, "w4a16", 128)
+        return pkg.QuantLinear.quantise(pkg.parallel.shard_weight(name, w, tp_rank, tp_world), "w4a16", 128)
 
-    weights["embedding"] = make(cfg["vocab"], cfg["d_model"])
-    weights["lm_head"] = make(cfg["vocab"], cfg["d_model"])
+    weights["embedding"] = make("embedding", cfg["vocab"], cfg["d_model"])
+    weights["lm_head"] = make("lm_head", cfg["vocab"], cfg["d_model"])
     weights["final_norm"] = torch.ones(cfg["d_model"], device="cuda")
     for l in range(cfg["n_layers"]):
         for name, (n, k) in linear_shapes(cfg).items():
-            weights[f"layers.{l}.{name}"] = make(n, k)
+            weights[f"layers.{l}.{name}"] = make(f"layers.{l}.{name}", n, k)
         weights[f"layers.{l}.norm1"] = torch.ones(cfg["d_model"], device="cuda")
         weights[f"layers.{l}.norm2"] = torch.ones(cfg["d_model"], device="cuda")
     mc = pkg.ModelConfig(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"],
                          cfg["ffn_hidden"], cfg["vocab"], cfg["max_seq"], 1e-5, 10000.0, False)
+    if tp_world > 1:
+        mc = pkg.parallel.shard_config(mc, tp_world)
     return mc, weights
 
 
@@ -235,11 +238,13 @@ def main():
         print(json.dumps(line))
         return 0
 
+    tp = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    mc, weights = build_large(pkg, torch, cfg)
-    model = pkg.AarambhModel(mc, weights, dtype=torch.bfloat16, max_tokens=max(PROMPT, B))
+        tp = pkg.TensorParallel.from_torch_distributed()
+    mc, weights = build_large(pkg, torch, cfg, tp_rank=rank, tp_world=world)
+    model = pkg.AarambhModel(mc, weights, dtype=torch.bfloat16, max_tokens=max(PROMPT, B), tp=tp)
     cache = model.empty_kv_cache_with_capacity(PROMPT + NEW_TOKENS + args.warmup + args.steps + 8, batch=B, dtype="int8")
     gen = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg["vocab"], (B, PROMPT), generator=gen)
@@ -297,7 +302,9 @@ def main():
             host_step()
         e2e_s = (time.perf_counter() - t0) / e2e_steps
 
-    gemv_s, gemv_launches, gemv_bytes = time_gemv_only(pkg, torch, weights, cfg, max(8, args.steps // 4), stream)
+    local_cfg = dict(cfg, n_heads=cfg["n_heads"] // world, n_kv_heads=cfg["n_kv_heads"] // world,
+                     ffn_hidden=cfg["ffn_hidden"] // world)
+    gemv_s, gemv_launches, gemv_bytes = time_gemv_only(pkg, torch, weights, local_cfg, max(8, args.steps // 4), stream)
     status = pkg.device_status()
     peaks = {}
     try:
@@ -307,8 +314,10 @@ def main():
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = gemv_bytes / gemv_s / 1e9
     ctx_mid = PROMPT + max(args.warmup, 3) + args.steps // 2
-    step_bytes = step_weight_bytes(cfg) + B * ctx_mid * kv_bytes_per_token(cfg)
-    launches_per_step = 1 + cfg["n_layers"] * 14 + 3 + 1
+    # per GPU: a rank reads its 1/world share of the layer weights, head and KV
+    step_bytes = (step_weight_bytes(cfg) + B * ctx_mid * kv_bytes_per_token(cfg)) // world
+    # embedding, per layer {norm, qkv, attention, o, norm, gate|up+SwiGLU, down}, final norm, head, argmax, commit
+    launches_per_step = 1 + cfg["n_layers"] * (7 if world == 1 else 11) + 3 + 1
 
     line = {
         "metric": "INT4 decode tok/s", "value": round(B * 1e3 / ms_per_step, 2), "unit": "tokens/s",

@@ -279,6 +279,26 @@ int ab2_model_set_norm(ab2_model *m, int layer, int which, const float *weight);
  * workspace. */
 int ab2_model_finalize(ab2_model *m);
 int ab2_model_rope_tables(const ab2_model *m, const float **cos_dev, const float **sin_dev);
+
+/* ---- tensor parallelism ------------------------------------------------------
+ * Megatron-style sharding of the decoder over the GPUs of one box, one process
+ * per GPU.  The reference is data-parallel only; what is kept from it is the
+ * bootstrap convention of its NCCL path (a 128-byte unique id made by rank 0
+ * and handed to every rank, crates/aarambh-studio-train/src/distributed.rs:
+ * 526-591) and the sum all-reduce (distributed.rs:494-503).
+ * A rank's model is created with its LOCAL head counts and FFN width
+ * (n_heads / world, n_kv_heads / world, ffn_hidden / world; d_model and vocab
+ * whole): wq/wk/wv/w_gate/w_up hold the rank's rows (column parallel), wo and
+ * w_down the rank's input columns (row parallel; the split falls on group
+ * boundaries), lm_head the rank's vocab / world rows, the embedding is whole.
+ * After wo and w_down the partial sums are all-reduced; the logits shards are
+ * all-gathered.  ab2_model_set_tp must precede the lm_head and ab2_model_finalize. */
+int ab2_tp_unique_id(void *id128_host);
+int ab2_tp_create(ab2_tp **out, int rank, int world, const void *id128_host);
+int ab2_tp_destroy(ab2_tp *tp);
+/* In-place sum over ranks of `count` elements (NCCL all-reduce). */
+int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype dtype, ab2_stream stream);
+int ab2_model_set_tp(ab2_model *m, ab2_tp *tp);
 /* AarambhModel::forward_with_cache (model.rs:508-587; nrows = 1, S = prompt
  * length) and forward_decode_batch (model.rs:590-641; S = 1): ids_dev
  * [nrows, S] u32, rows row0..row0+nrows-1 of the cache.  offsets_host [nrows]

@@ -1,0 +1,97 @@
+"""Tensor-parallel decoder against the single-GPU decoder (needs 2 GPUs; skipped
+otherwise): same seeded weights, sharded over 2 NCCL ranks, logits within 1e-2
+relative and the same greedy tokens."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, head_dim=128, ffn_hidden=1024, vocab=2048, max_seq=64)
+SHAPES = {"wq": (512, 512), "wk": (256, 512), "wv": (256, 512), "wo": (512, 512), "w_gate": (1024, 512),
+          "w_up": (1024, 512), "w_down": (512, 1024)}
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _build(pkg, rank, world, tp):
+    gen = torch.Generator(device="cuda").manual_seed(11)
+
+    def dense(shape):
+        return torch.randn(shape, generator=gen, device="cuda") * 0.05
+
+    def pack(name, w):
+        return pkg.QuantLinear.quantise(pkg.parallel.shard_weight(name, w, rank, world), "w4a16", 128)
+
+    weights = {"embedding": pack("embedding", dense((CFG["vocab"], CFG["d_model"]))),
+               "lm_head": pack("lm_head", dense((CFG["vocab"], CFG["d_model"]))),
+               "final_norm": torch.ones(CFG["d_model"], device="cuda")}
+    for l in range(CFG["n_layers"]):
+        for n, s in SHAPES.items():
+            weights[f"layers.{l}.{n}"] = pack(f"layers.{l}.{n}", dense(s))
+        weights[f"layers.{l}.norm1"] = torch.ones(CFG["d_model"], device="cuda")
+        weights[f"layers.{l}.norm2"] = torch.ones(CFG["d_model"], device="cuda")
+    cfg = pkg.ModelConfig(CFG["n_layers"], CFG["d_model"], CFG["n_heads"], CFG["n_kv_heads"], CFG["head_dim"],
+                          CFG["ffn_hidden"], CFG["vocab"], CFG["max_seq"], 1e-5, 10000.0, False)
+    if world > 1:
+        cfg = pkg.parallel.shard_config(cfg, world)
+    return pkg.AarambhModel(cfg, weights, dtype=torch.bfloat16, max_tokens=32, tp=tp)
+
+
+def _run(model, steps=6):
+    ids = torch.tensor([[3, 99, 1500, 7, 42]])
+    cache = model.empty_kv_cache_with_capacity(32, dtype="int8")
+    logits = [model.forward_with_cache(ids, 0, cache, last_only=True).float().cpu().numpy().ravel()]
+    toks = [int(np.argmax(logits[0]))]
+    for i in range(steps):
+        lg = model.forward_decode_batch(torch.tensor([[toks[-1]]]), [5 + i], cache).float().cpu().numpy().ravel()
+        logits.append(lg)
+        toks.append(int(np.argmax(lg)))
+    return np.stack(logits), toks
+
+
+def _worker(rank, world, port, out):
+    import torch.distributed as dist
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from __graft_entry__ import import_package
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        pkg = import_package()
+        tp = pkg.TensorParallel.from_torch_distributed()
+        logits, toks = _run(_build(pkg, rank, world, tp))
+        if rank == 0:
+            ref_logits, ref_toks = _run(_build(pkg, 0, 1, None))
+            err = float(np.abs(logits - ref_logits).max() / np.abs(ref_logits).max())
+            out.put(("result", err, toks, ref_toks))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        out.put(("error", rank, repr(e)))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_matches_single_gpu():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    msg = out.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+    assert msg[0] == "result", msg
+    _, err, toks, ref_toks = msg
+    assert err < 1e-2, err
+    assert toks == ref_toks
