@@ -130,7 +130,9 @@ constexpr int W4_STAGE_WORDS = W4_GROUPS_PER_STAGE * W4_BLOCK_WORDS;
 // residual plus the projection (W4_EPI_ADD; `resid` may alias `y`), or
 // silu(gate) * up for a weight whose 16-row tiles hold 8 gate rows followed by
 // the 8 matching up rows (W4_EPI_SWIGLU; y is [M][N/2]).
-enum { W4_EPI_STORE = 0, W4_EPI_ADD = 1, W4_EPI_SWIGLU = 2 };
+// W4_EPI_F32 stores the f32 sums ([M][N] floats at `y`): the partial result of a
+// row-parallel shard, summed across ranks before it is rounded.
+enum { W4_EPI_STORE = 0, W4_EPI_ADD = 1, W4_EPI_SWIGLU = 2, W4_EPI_F32 = 3 };
 
 template <int NT, int EPI>
 __global__ void __launch_bounds__(256)
@@ -335,9 +337,13 @@ gemv_w4a16_stream_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *_
 #pragma unroll
                     for (int w = 0; w < 8; ++w) v += red[buf][w][row][tok];
                     const size_t o = (size_t)tok * N + row0 + row;
-                    if (EPI == W4_EPI_ADD)  // residual + bf16(projection), as residual + x does
-                        v = __bfloat162float(resid[o]) + __bfloat162float(__float2bfloat16_rn(v));
-                    y[o] = __float2bfloat16_rn(v);
+                    if (EPI == W4_EPI_F32) {  // unrounded partial sum of a row-parallel shard
+                        reinterpret_cast<float *>(y)[o] = v;
+                    } else {
+                        if (EPI == W4_EPI_ADD)  // residual + bf16(projection), as residual + x does
+                            v = __bfloat162float(resid[o]) + __bfloat162float(__float2bfloat16_rn(v));
+                        y[o] = __float2bfloat16_rn(v);
+                    }
                 }
             }
             __syncwarp();

@@ -24,6 +24,7 @@ int device_status_word(int **out);
 bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype);
 int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s);
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
+int qlinear_w4a16_mma_f32(const ab2_qweight *w, const void *x, int M, float *y, cudaStream_t s);
 }
 extern "C" int ab2_qweight_interleave_gate_up(ab2_qweight **out, const ab2_qweight *gate, const ab2_qweight *up);
 
@@ -48,6 +49,7 @@ struct ab2_model {
     bool finalized;
     bool fused_epilogues;  // W4A16 + bf16: residual add and SwiGLU ride the GEMV epilogues
     ab2_tp *tp;            // tensor-parallel context (borrowed), or null
+    float *proj32;            // tensor-parallel: f32 partial sums of the row-parallel projections
     void *lg_local, *lg_all;  // tensor-parallel logits: this rank's vocabulary shard / all shards
     // workspace, sized for max_tokens
     void *x, *xn, *qkv, *attn, *proj, *gu, *hid;
@@ -84,6 +86,13 @@ template <typename T>
 __global__ void gather_last_kernel(const T *in, T *out, int S, int d) {
     const T *src = in + ((size_t)blockIdx.x * S + (S - 1)) * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)blockIdx.x * d + i] = src[i];
+}
+
+// x = x + round(p), p the all-reduced f32 projection: the residual add of
+// TransformerBlock::forward with the projection rounded to bf16 once, after the sum.
+__global__ void add_f32_projection_kernel(__nv_bfloat16 *x, const float *p, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(__float2bfloat16_rn(p[i])));
 }
 
 // [world][rows][vn] (all-gathered vocabulary shards) -> [rows][world * vn]
@@ -151,19 +160,28 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         const bool tp = m->tp && m->tp->world > 1;
         if (tp) {
             // row-parallel O and down produce partial sums: all-reduce, then the residual add
-            STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
-            STEP(tp_all_reduce(m->tp, m->proj, (size_t)T * d, m->dtype, s));
-            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
-            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+            const size_t nd = (size_t)T * d;
             if (m->fused_epilogues) {
+                STEP(qlinear_w4a16_mma_f32(L.part[3], m->attn, T, m->proj32, s));
+                STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
+                add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
+                STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
                 STEP(qlinear_w4a16_mma_swiglu(L.wgu, m->xn, T, m->hid, s));
+                STEP(qlinear_w4a16_mma_f32(L.part[6], m->hid, T, m->proj32, s));
+                STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
+                add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
+                AB2_LAUNCH_CHECK();
             } else {
+                STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
+                STEP(tp_all_reduce(m->tp, m->proj, nd, m->dtype, s));
+                STEP(launch_add(m->x, m->proj, m->x, nd, m->dtype, s));
+                STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
                 STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
                 STEP(launch_swiglu_fused(m->gu, m->hid, T, c.ffn_hidden, m->dtype, s));
+                STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
+                STEP(tp_all_reduce(m->tp, m->proj, nd, m->dtype, s));
+                STEP(launch_add(m->x, m->proj, m->x, nd, m->dtype, s));
             }
-            STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
-            STEP(tp_all_reduce(m->tp, m->proj, (size_t)T * d, m->dtype, s));
-            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
         } else if (m->fused_epilogues) {
             STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
             STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
@@ -263,7 +281,7 @@ AB2_API int ab2_model_create(ab2_model **out, const ab2_model_config *cfg, ab2_d
     m->finalized = false;
     m->x = m->xn = m->qkv = m->attn = m->proj = m->gu = m->hid = nullptr;
     m->positions = nullptr; m->positions_host = nullptr;
-    m->tp = nullptr; m->lg_local = m->lg_all = nullptr; m->fused_epilogues = false;
+    m->tp = nullptr; m->lg_local = m->lg_all = nullptr; m->proj32 = nullptr; m->fused_epilogues = false;
     *out = m;
     return AB2_OK;
 }
@@ -277,7 +295,7 @@ AB2_API int ab2_model_destroy(ab2_model *m) {
     }
     cudaFree(m->final_norm); cudaFree(m->cos_t); cudaFree(m->sin_t);
     cudaFree(m->x); cudaFree(m->xn); cudaFree(m->qkv); cudaFree(m->attn); cudaFree(m->proj);
-    cudaFree(m->gu); cudaFree(m->hid); cudaFree(m->positions); cudaFree(m->lg_local); cudaFree(m->lg_all);
+    cudaFree(m->gu); cudaFree(m->hid); cudaFree(m->positions); cudaFree(m->lg_local); cudaFree(m->lg_all); cudaFree(m->proj32);
     if (m->positions_host) cudaFreeHost(m->positions_host);
     delete m;
     return AB2_OK;
@@ -377,6 +395,7 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
         if (m->tp && m->tp->world > 1) {
             AB2_CUDA(cudaMalloc(&m->lg_local, T * (c.vocab / m->tp->world) * esz));
             AB2_CUDA(cudaMalloc(&m->lg_all, T * c.vocab * esz));
+            AB2_CUDA(cudaMalloc((void **)&m->proj32, T * c.d_model * 4));
         }
         AB2_CUDA(cudaMalloc((void **)&m->positions, (size_t)m->max_tokens * 4));
         AB2_CUDA(cudaMallocHost((void **)&m->positions_host, (size_t)m->max_tokens * 4));

@@ -109,7 +109,8 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     for (int m0 = 0; m0 < M; m0 += 16) {
         const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;
-        __nv_bfloat16 *yp = (__nv_bfloat16 *)y + (size_t)m0 * out_n;
+        __nv_bfloat16 *yp = EPI == W4_EPI_F32 ? (__nv_bfloat16 *)((float *)y + (size_t)m0 * out_n)
+                                              : (__nv_bfloat16 *)y + (size_t)m0 * out_n;
         const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
         int mv = M - m0 < 16 ? M - m0 : 16;
         cudaError_t e;
@@ -127,6 +128,10 @@ int qlinear_w4a16_mma(const ab2_qweight *w, const void *x, int M, void *y, cudaS
 // y = resid + x . W^T (resid may be y)
 int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s) {
     return launch_w4a16_stream<W4_EPI_ADD>(w, x, M, y, resid, s);
+}
+// y[M][N] f32 = x . W^T, unrounded (partial sums of a row-parallel shard)
+int qlinear_w4a16_mma_f32(const ab2_qweight *w, const void *x, int M, float *y, cudaStream_t s) {
+    return launch_w4a16_stream<W4_EPI_F32>(w, x, M, y, nullptr, s);
 }
 // y[M][N/2] = silu(gate) * up for a gate|up weight interleaved in 8-row halves
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
