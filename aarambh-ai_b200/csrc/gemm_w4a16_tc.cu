@@ -1,0 +1,348 @@
+// W4A16 (group 128, bf16) GEMM for many tokens (prefill, batched decode) on the
+// 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory.
+//
+//   Y[M, N] = X[M, K] . W^T,  W packed 4-bit in tile-major blocks (w4a16_layout.cuh)
+//
+// The product is formed transposed: the 128 output channels of a tile are the M
+// dimension of the MMA (operand A = dequantised weights), the tokens its N
+// dimension (operand B = activations), so any token count is a legal N and the
+// weights are dequantised once per (channel tile, token tile).  One CTA per SM,
+// persistent over tiles, warp-specialised:
+//   warp 0      producer: bulk copies of packed weight blocks into a ring, TMA
+//               tile loads of X (128-byte swizzle) into the operand-B stages
+//   warp 1      allocates tensor memory, issues tcgen05.mma (K = 16 per
+//               instruction, 64 per stage), commits stage / accumulator barriers
+//   warps 2-5   dequantise: thread = output channel; nibbles -> bf16 (128 + q by
+//               one logic op, minus (128 + z) exactly, times the bf16 scale, i.e.
+//               the round-to-nearest bf16 of (q - z) * s) written into the
+//               operand-A stage in the canonical K-major 128-byte-swizzle layout
+//   warps 6-9   epilogue: tcgen05.ld of the accumulator, bf16 stores of Y
+// Every wait on an mbarrier is bounded; on a time-out the CTA records
+// AB2_ERR_TIMEOUT, stops issuing work, still frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "w4a16_layout.cuh"
+
+using namespace ab2;
+
+namespace ab2 {
+int device_status_word(int **out);
+int device_sm_count();
+namespace {
+
+constexpr int TC_STAGES = 4;          // operand stages of 64 K-elements
+constexpr int TC_WSLOTS = 4;          // packed-weight ring slots (one quantisation group each)
+constexpr int TC_BLOCK_WORDS = 272;   // 16 rows x 16 code words + 16 parameter words
+constexpr int TC_WSLOT_BYTES = 8 * TC_BLOCK_WORDS * 4;  // 8 row tiles of 16 = 128 channels
+constexpr int TC_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
+constexpr int TC_THREADS = 320;
+
+__device__ __forceinline__ uint32_t sptr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+struct TcShared {
+    uint64_t wfull[TC_WSLOTS], wempty[TC_WSLOTS];
+    uint64_t xfull[TC_STAGES], afull[TC_STAGES], sempty[TC_STAGES];
+    uint64_t accfull, accempty;
+    uint32_t tmem_base;
+    int failed;
+};
+
+__device__ __forceinline__ void bar_init(uint64_t *b, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(sptr(b)), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint64_t *b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(sptr(b)) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t *b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(sptr(b)), "r"(bytes) : "memory");
+}
+// Bounded wait; also gives up as soon as another warp of the CTA has failed.
+__device__ __forceinline__ bool bar_wait(uint64_t *b, uint32_t parity, volatile int *failed) {
+    const uint32_t addr = sptr(b);
+    for (int spin = 0; spin < (1 << 20); ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 1023) == 1023 && *failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+
+__device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+                     "r"(sptr(dst)), "l"(src), "r"(bytes), "r"(sptr(bar)) : "memory");
+}
+// 2-D tile load: coordinates (k element, token row); completion counted on `bar`.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
+            "r"(sptr(dst)), "l"(map), "r"(sptr(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: 8-row groups are
+// 1024 bytes apart, the start address advances by 32 bytes per K = 16 step.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major): 1
+    d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;             // descriptor version
+    d |= (uint64_t)2 << 61;             // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::
+            "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(sptr(bar)) : "memory");
+}
+
+__device__ __forceinline__ uint32_t bf16x2_add_(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_mul_(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+template <int NTOK>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CUtensorMap xmap,
+                     __nv_bfloat16 *__restrict__ y, int N, int K, int M, int *status) {
+    constexpr int B_BYTES = NTOK * 128;
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((128u >> 4) << 24);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *a_st = smem;                                   // [TC_STAGES][TC_A_BYTES]
+    uint8_t *b_st = a_st + TC_STAGES * TC_A_BYTES;          // [TC_STAGES][B_BYTES]
+    uint8_t *w_ring = b_st + TC_STAGES * B_BYTES;           // [TC_WSLOTS][TC_WSLOT_BYTES]
+    TcShared *sh = (TcShared *)(w_ring + TC_WSLOTS * TC_WSLOT_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = K >> 7, tiles16 = (N + 15) >> 4;
+    const int n_tiles = (N + 127) >> 7, m_tiles = (M + NTOK - 1) / NTOK;
+    const int items = n_tiles * m_tiles;
+    volatile int *failed = &sh->failed;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TC_WSLOTS; ++i) { bar_init(&sh->wfull[i], 1); bar_init(&sh->wempty[i], 128); }
+        for (int i = 0; i < TC_STAGES; ++i) { bar_init(&sh->xfull[i], 1); bar_init(&sh->afull[i], 128); bar_init(&sh->sempty[i], 1); }
+        bar_init(&sh->accfull, 1);
+        bar_init(&sh->accempty, 4);
+        sh->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {  // tensor-memory allocation is a whole-warp operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(sptr(&sh->tmem_base)), "r"((uint32_t)NTOK));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------- producer
+        if (lane == 0) {
+            uint32_t wuse = 0, suse = 0;
+            for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
+                const int nt = it / m_tiles, mt = it % m_tiles;
+                const int nblk = min(8, tiles16 - nt * 8);
+                for (int g = 0; g < G && !*failed; ++g, ++wuse) {
+                    const int ws = wuse % TC_WSLOTS;
+                    if (!bar_wait(&sh->wempty[ws], ((wuse / TC_WSLOTS) & 1) ^ 1, failed)) break;
+                    bar_expect_tx(&sh->wfull[ws], (uint32_t)nblk * TC_BLOCK_WORDS * 4);
+                    for (int b = 0; b < nblk; ++b)
+                        bulk_copy(w_ring + ws * TC_WSLOT_BYTES + b * TC_BLOCK_WORDS * 4,
+                                  wt + ((size_t)(nt * 8 + b) * G + g) * TC_BLOCK_WORDS, TC_BLOCK_WORDS * 4, &sh->wfull[ws]);
+                    for (int half = 0; half < 2; ++half, ++suse) {
+                        const int s = suse % TC_STAGES;
+                        if (!bar_wait(&sh->sempty[s], ((suse / TC_STAGES) & 1) ^ 1, failed)) break;
+                        bar_expect_tx(&sh->xfull[s], B_BYTES);
+                        tma_load_2d(b_st + s * B_BYTES, &xmap, g * 128 + half * 64, mt * NTOK, &sh->xfull[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issue
+        uint32_t suse = 0, tuse = 0;
+        for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x, ++tuse) {
+            if (!bar_wait(&sh->accempty, (tuse & 1) ^ 1, failed)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            for (int ks = 0; ks < 2 * G && !*failed; ++ks, ++suse) {
+                const int s = suse % TC_STAGES;
+                const uint32_t par = (suse / TC_STAGES) & 1;
+                if (!bar_wait(&sh->xfull[s], par, failed)) break;
+                if (!bar_wait(&sh->afull[s], par, failed)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (lane == 0) {
+                    const uint32_t a0 = sptr(a_st + s * TC_A_BYTES), b0 = sptr(b_st + s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (ks | k) != 0);
+                    umma_commit(&sh->sempty[s]);  // frees both operand stages when the MMAs retire
+                }
+                __syncwarp();
+            }
+            if (lane == 0) umma_commit(&sh->accfull);
+            __syncwarp();
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------- dequantise
+        const int t = threadIdx.x - 64;  // output channel within the 128-channel tile
+        const int blk = t >> 4, r = t & 15;
+        uint32_t wuse = 0, suse = 0;
+        uint32_t k_mask = 0x000F000Fu, k_magic = 0x43004300u;
+        asm volatile("" : "+r"(k_mask), "+r"(k_magic));
+        for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
+            for (int g = 0; g < G && !*failed; ++g, ++wuse) {
+                const int ws = wuse % TC_WSLOTS;
+                if (!bar_wait(&sh->wfull[ws], (wuse / TC_WSLOTS) & 1, failed)) break;
+                const uint32_t *bw = (const uint32_t *)(w_ring + ws * TC_WSLOT_BYTES) + blk * TC_BLOCK_WORDS;
+                uint4 pw[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pw[i] = *reinterpret_cast<const uint4 *>(bw + r * 16 + i * 4);
+                const uint32_t pr = bw[256 + r];
+                bar_arrive(&sh->wempty[ws]);
+                const uint32_t sc2 = __byte_perm(pr, pr, 0x1010);  // bf16x2 (scale, scale)
+                const uint32_t nz2 = __byte_perm(pr, pr, 0x3232);  // bf16x2 -(128 + z)
+#pragma unroll
+                for (int half = 0; half < 2; ++half, ++suse) {
+                    const int s = suse % TC_STAGES;
+                    if (!bar_wait(&sh->sempty[s], ((suse / TC_STAGES) & 1) ^ 1, failed)) break;
+                    uint8_t *arow = a_st + s * TC_A_BYTES + t * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {  // chunk c = 8 consecutive k = one code word
+                        const uint4 q4 = pw[half * 2 + (c >> 2)];
+                        const uint32_t word = (c & 3) == 0 ? q4.x : (c & 3) == 1 ? q4.y : (c & 3) == 2 ? q4.z : q4.w;
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t v;
+                            const uint32_t shv = j ? (word >> (4 * j)) : word;
+                            asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(v) : "r"(shv), "r"(k_mask), "r"(k_magic));
+                            o[j] = bf16x2_mul_(bf16x2_add_(v, nz2), sc2);
+                        }
+                        *reinterpret_cast<uint4 *>(arow + ((c ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    bar_arrive(&sh->afull[s]);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------- epilogue
+        const int quad = warp & 3;
+        uint32_t tuse = 0;
+        for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x, ++tuse) {
+            const int nt = it / m_tiles, mt = it % m_tiles;
+            if (!bar_wait(&sh->accfull, tuse & 1, failed)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int n = nt * 128 + quad * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < NTOK / 32; ++c) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = mt * NTOK + c * 32 + j;
+                        if (tok < M) y[(size_t)tok * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(&sh->accempty);
+        }
+    }
+
+    // ---- teardown: every warp arrives here (all waits are bounded)
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0 && sh->failed) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)NTOK));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_x_map(CUtensorMap *map, const void *x, int M, int K, int ntok) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        AB2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        AB2_REQUIRE(fn != nullptr && qres == cudaDriverEntryPointSuccess, AB2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is unavailable");
+        encode = (EncodeTiledFn)fn;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)ntok};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    AB2_REQUIRE(r == CUDA_SUCCESS, AB2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return AB2_OK;
+}
+
+template <int NTOK>
+int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+    int *status = nullptr;
+    int rc = device_status_word(&status);
+    if (rc != AB2_OK) return rc;
+    CUtensorMap map;
+    rc = make_x_map(&map, x, M, w->K, NTOK);
+    if (rc != AB2_OK) return rc;
+    const size_t smem = 1024 + TC_STAGES * TC_A_BYTES + TC_STAGES * NTOK * 128 + TC_WSLOTS * TC_WSLOT_BYTES + sizeof(TcShared);
+    static bool configured = false;
+    if (!configured) {
+        AB2_CUDA(cudaFuncSetAttribute(gemm_w4a16_tc_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    const int items = ((w->N + 127) / 128) * ((M + NTOK - 1) / NTOK);
+    const int grid = std::min(items, device_sm_count());
+    gemm_w4a16_tc_kernel<NTOK><<<grid, TC_THREADS, smem, s>>>((const uint32_t *)w->codes, map, (__nv_bfloat16 *)y, w->N, w->K, M, status);
+    AB2_LAUNCH_CHECK();
+    return AB2_OK;
+}
+
+}  // namespace
+
+// Y[M][N] = X[M][K] . W^T on the tcgen05 path (W4A16, group 128, bf16).
+int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+    AB2_REQUIRE(((uintptr_t)x & 15) == 0 && (w->K * 2) % 16 == 0, AB2_ERR_BAD_ALIGN, "activations must be 16-byte aligned");
+    if (M <= 48) return launch_tc<32>(w, x, M, y, s);
+    return launch_tc<128>(w, x, M, y, s);
+}
+
+}  // namespace ab2

@@ -95,6 +95,17 @@ __global__ void add_f32_projection_kernel(__nv_bfloat16 *x, const float *p, size
     if (i < n) x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(__float2bfloat16_rn(p[i])));
 }
 
+// SwiGLU over the output of the interleaved gate|up weight: columns come in
+// blocks of 16 = 8 gate values followed by the 8 matching up values.
+__global__ void swiglu_interleaved8_kernel(const __nv_bfloat16 *gu, __nv_bfloat16 *out, int ffn, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    size_t tok = i / ffn;
+    int j = (int)(i % ffn);
+    const __nv_bfloat16 *row = gu + tok * 2 * (size_t)ffn + (size_t)(j >> 3) * 16 + (j & 7);
+    out[i] = __float2bfloat16_rn(swiglu_value(__bfloat162float(row[0]), __bfloat162float(row[8])));
+}
+
 // [world][rows][vn] (all-gathered vocabulary shards) -> [rows][world * vn]
 template <typename T>
 __global__ void reorder_shards_kernel(const T *in, T *out, int rows, int vn, int world) {
@@ -182,6 +193,19 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
                 STEP(tp_all_reduce(m->tp, m->proj, nd, m->dtype, s));
                 STEP(launch_add(m->x, m->proj, m->x, nd, m->dtype, s));
             }
+        } else if (m->fused_epilogues && T > 16) {
+            // many tokens: tensor-core GEMMs, then the element-wise steps
+            STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
+            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+            STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
+            {
+                size_t n = (size_t)T * c.ffn_hidden;
+                swiglu_interleaved8_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>((const __nv_bfloat16 *)m->gu, (__nv_bfloat16 *)m->hid, c.ffn_hidden, n);
+                AB2_LAUNCH_CHECK();
+            }
+            STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
+            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
         } else if (m->fused_epilogues) {
             STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
             STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));

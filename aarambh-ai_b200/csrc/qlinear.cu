@@ -138,8 +138,14 @@ int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y
     return launch_w4a16_stream<W4_EPI_SWIGLU>(w, x, M, y, nullptr, s);
 }
 
+int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
+
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {
-    if (qlinear_w4a16_mma_eligible(w, dtype)) return qlinear_w4a16_mma(w, x, M, y, s);
+    if (qlinear_w4a16_mma_eligible(w, dtype)) {
+        // up to 16 tokens: HBM-bound GEMV on the warp MMA; beyond: tcgen05 GEMM
+        if (M <= 16) return qlinear_w4a16_mma(w, x, M, y, s);
+        return qlinear_w4a16_tc(w, x, M, y, s);
+    }
     return qlinear_generic(w, x, M, dtype, y, s);
 }
 

@@ -85,3 +85,18 @@ def test_shape_and_dtype_errors():
     with pytest.raises(p.Ab2Error) as e:
         lin(torch.zeros(2, 64, device="cuda", dtype=torch.float64))
     assert e.value.status == -3
+
+
+@pytest.mark.parametrize("M", [17, 32, 64, 200, 512])
+@pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 400)])
+def test_w4a16_many_tokens_tensor_core_gemm(M, K, N):
+    """More than 16 tokens take the tcgen05 GEMM: against dequantise-then-matmul
+    within 1e-2 relative (the weights enter the MMA rounded to bf16)."""
+    rng = np.random.default_rng(6)
+    qw, scales, qz = make_w4a16(rng, N, K)
+    lin = pkg().QuantLinear.from_w4a16_gptq(qw, scales, qz, N, K, 128)
+    dense = orc.dequant_w4a16(qw, scales, qz, N, K, 128)
+    x = orc.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    got = run(lin, x, torch.bfloat16)
+    assert pkg().device_status() == 0
+    assert rel_err(got, orc.linear(x, dense)) < TOL_BF16
