@@ -33,7 +33,7 @@ int device_status_word(int **out);
 int device_sm_count();
 namespace {
 
-constexpr int TC_STAGES = 4;          // operand stages of 64 K-elements
+constexpr int TC_MAX_STAGES = 4;      // operand stages of 64 K-elements (3 for 256-token tiles)
 constexpr int TC_WSLOTS = 4;          // packed-weight ring slots (one quantisation group each)
 constexpr int TC_BLOCK_WORDS = 272;   // 16 rows x 16 code words + 16 parameter words
 constexpr int TC_WSLOT_BYTES = 8 * TC_BLOCK_WORDS * 4;  // 8 row tiles of 16 = 128 channels
@@ -44,8 +44,8 @@ __device__ __forceinline__ uint32_t sptr(const void *p) { return (uint32_t)__cvt
 
 struct TcShared {
     uint64_t wfull[TC_WSLOTS], wempty[TC_WSLOTS];
-    uint64_t xfull[TC_STAGES], afull[TC_STAGES], sempty[TC_STAGES];
-    uint64_t accfull, accempty;
+    uint64_t xfull[TC_MAX_STAGES], afull[TC_MAX_STAGES], sempty[TC_MAX_STAGES];
+    uint64_t accfull[2], accempty[2];  // two accumulators: the epilogue of a tile overlaps the next tile's MMAs
     uint32_t tmem_base;
     int failed;
 };
@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CUtensorMap xmap,
                      __nv_bfloat16 *__restrict__ y, int N, int K, int M, int *status) {
     constexpr int B_BYTES = NTOK * 128;
+    constexpr int TC_STAGES = NTOK > 128 ? 3 : 4;
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((128u >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -140,14 +141,13 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
     if (threadIdx.x == 0) {
         for (int i = 0; i < TC_WSLOTS; ++i) { bar_init(&sh->wfull[i], 1); bar_init(&sh->wempty[i], 128); }
         for (int i = 0; i < TC_STAGES; ++i) { bar_init(&sh->xfull[i], 1); bar_init(&sh->afull[i], 128); bar_init(&sh->sempty[i], 1); }
-        bar_init(&sh->accfull, 1);
-        bar_init(&sh->accempty, 4);
+        for (int i = 0; i < 2; ++i) { bar_init(&sh->accfull[i], 1); bar_init(&sh->accempty[i], 4); }
         sh->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     if (warp == 1) {  // tensor-memory allocation is a whole-warp operation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(sptr(&sh->tmem_base)), "r"((uint32_t)NTOK));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(sptr(&sh->tmem_base)), "r"((uint32_t)(2 * NTOK)));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -182,8 +182,10 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         // ---------------------------------------------------------- MMA issue
         uint32_t suse = 0, tuse = 0;
         for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x, ++tuse) {
-            if (!bar_wait(&sh->accempty, (tuse & 1) ^ 1, failed)) break;
+            const int ab = tuse & 1;
+            if (!bar_wait(&sh->accempty[ab], ((tuse >> 1) & 1) ^ 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t tacc = tmem + (uint32_t)(ab * NTOK);
             for (int ks = 0; ks < 2 * G && !*failed; ++ks, ++suse) {
                 const int s = suse % TC_STAGES;
                 const uint32_t par = (suse / TC_STAGES) & 1;
@@ -194,12 +196,12 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                     const uint32_t a0 = sptr(a_st + s * TC_A_BYTES), b0 = sptr(b_st + s * B_BYTES);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (ks | k) != 0);
+                        umma_bf16(tacc, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (ks | k) != 0);
                     umma_commit(&sh->sempty[s]);  // frees both operand stages when the MMAs retire
                 }
                 __syncwarp();
             }
-            if (lane == 0) umma_commit(&sh->accfull);
+            if (lane == 0) umma_commit(&sh->accfull[ab]);
             __syncwarp();
         }
     } else if (warp < 6) {
@@ -251,13 +253,14 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         uint32_t tuse = 0;
         for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x, ++tuse) {
             const int nt = it / m_tiles, mt = it % m_tiles;
-            if (!bar_wait(&sh->accfull, tuse & 1, failed)) break;
+            const int ab = tuse & 1;
+            if (!bar_wait(&sh->accfull[ab], (tuse >> 1) & 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int n = nt * 128 + quad * 32 + lane;
 #pragma unroll 1
             for (int c = 0; c < NTOK / 32; ++c) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * NTOK + c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
@@ -277,7 +280,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) bar_arrive(&sh->accempty);
+            if (lane == 0) bar_arrive(&sh->accempty[ab]);
         }
     }
 
@@ -287,7 +290,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
     if (threadIdx.x == 0 && sh->failed) atomicExch(status, (int)AB2_ERR_TIMEOUT);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)NTOK));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)(2 * NTOK)));
     }
 }
 
@@ -323,7 +326,8 @@ int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t 
     CUtensorMap map;
     rc = make_x_map(&map, x, M, w->K, NTOK);
     if (rc != AB2_OK) return rc;
-    const size_t smem = 1024 + TC_STAGES * TC_A_BYTES + TC_STAGES * NTOK * 128 + TC_WSLOTS * TC_WSLOT_BYTES + sizeof(TcShared);
+    constexpr int stages = NTOK > 128 ? 3 : 4;
+    const size_t smem = 1024 + stages * TC_A_BYTES + stages * NTOK * 128 + TC_WSLOTS * TC_WSLOT_BYTES + sizeof(TcShared);
     static bool configured = false;
     if (!configured) {
         AB2_CUDA(cudaFuncSetAttribute(gemm_w4a16_tc_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -342,7 +346,8 @@ int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t 
 int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
     AB2_REQUIRE(((uintptr_t)x & 15) == 0 && (w->K * 2) % 16 == 0, AB2_ERR_BAD_ALIGN, "activations must be 16-byte aligned");
     if (M <= 48) return launch_tc<32>(w, x, M, y, s);
-    return launch_tc<128>(w, x, M, y, s);
+    if (M <= 1024) return launch_tc<128>(w, x, M, y, s);
+    return launch_tc<256>(w, x, M, y, s);
 }
 
 }  // namespace ab2

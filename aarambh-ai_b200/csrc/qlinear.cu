@@ -142,8 +142,10 @@ int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaSt
 
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {
     if (qlinear_w4a16_mma_eligible(w, dtype)) {
-        // up to 16 tokens: HBM-bound GEMV on the warp MMA; beyond: tcgen05 GEMM
-        if (M <= 16) return qlinear_w4a16_mma(w, x, M, y, s);
+        // Few tokens: HBM-bound GEMV on the warp MMA (16 tokens per pass).  The
+        // tcgen05 GEMM tiles 128 output channels per CTA, which leaves most SMs
+        // idle until the token count supplies the parallelism.
+        if (M <= 64) return qlinear_w4a16_mma(w, x, M, y, s);
         return qlinear_w4a16_tc(w, x, M, y, s);
     }
     return qlinear_generic(w, x, M, dtype, y, s);

@@ -87,7 +87,7 @@ def test_shape_and_dtype_errors():
     assert e.value.status == -3
 
 
-@pytest.mark.parametrize("M", [17, 32, 64, 200, 512])
+@pytest.mark.parametrize("M", [17, 64, 65, 200, 512, 1100])
 @pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 400)])
 def test_w4a16_many_tokens_tensor_core_gemm(M, K, N):
     """More than 16 tokens take the tcgen05 GEMM: against dequantise-then-matmul
