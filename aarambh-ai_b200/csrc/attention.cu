@@ -272,6 +272,19 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
     if (max_len <= 0)
         for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + pending);
     int nsplit = 1;
+    if (S == 1 && pending == 0 && kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8 &&
+        st.q_h == kv->hd && st.q_b == (long long)kv->h * kv->hd && st.o_h == st.q_h && st.o_b == st.q_b) {
+        // INT8 cache, head_dim 128: tensor-core flash-decode (attention_mma.cu)
+        const int want = (148 * 6 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
+        nsplit = std::max(1, std::min(std::min(want, (max_len + 63) / 64), kv->max_splits));
+        a.nsplit = nsplit;
+        int rc = attention_decode_mma_device(kv, layer, q, out, row0, nrows, scale, dtype, nsplit, kv->part_acc,
+                                             kv->part_ml, s);
+        if (rc != AB2_OK) return rc;
+        if (nsplit > 1) attn_merge_kernel<<<dim3(kv->h, nrows), kv->hd, 0, s>>>(a, kv->hd);
+        AB2_LAUNCH_CHECK();
+        return AB2_OK;
+    }
     if (S == 1) {
         int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
         int by_len = (max_len + 255) / 256;
@@ -402,8 +415,16 @@ AB2_API int ab2_attention_decode_static(const ab2_kv *kv, int layer, const void 
     a.st.o_b = a.st.q_b; a.st.o_s = 0; a.st.o_h = kv->hd;
     int max_len = 0;
     for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r]);
-    const int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
-    a.nsplit = std::max(1, std::min(std::min(want, (max_len + 255) / 256), AB2_KV_MAX_SPLITS));
+    // Same kernel choice and split count as ab2_attention_decode, so both entry
+    // points return the same bits.
+    const bool mma_path = kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8;
+    if (mma_path) {
+        const int want = (148 * 6 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
+        a.nsplit = std::max(1, std::min(std::min(want, (max_len + 63) / 64), AB2_KV_MAX_SPLITS));
+    } else {
+        const int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
+        a.nsplit = std::max(1, std::min(std::min(want, (max_len + 255) / 256), AB2_KV_MAX_SPLITS));
+    }
     // Partials are indexed by the absolute row, exactly as in the allocated scratch.
     const size_t parts = (size_t)(row0 + nrows) * kv->h * a.nsplit;
     const size_t need = parts * ((size_t)kv->hd + 2);
@@ -415,6 +436,14 @@ AB2_API int ab2_attention_decode_static(const ab2_kv *kv, int layer, const void 
     a.part_ml = g_static_attn_scratch_ptr[dev] + parts * kv->hd;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(a.nsplit, kv->kvh, nrows);
+    if (mma_path) {
+        rc = attention_decode_mma_device(kv, layer, q_dev, out_dev, row0, nrows, scale, dtype, a.nsplit, a.part_acc,
+                                         a.part_ml, s);
+        if (rc != AB2_OK) return rc;
+        if (a.nsplit > 1) attn_merge_kernel<<<dim3(kv->h, nrows), kv->hd, 0, s>>>(a, kv->hd);
+        AB2_LAUNCH_CHECK();
+        return AB2_OK;
+    }
     if (kv->dtype == AB2_KV_F32) rc = launch_split_hd<AB2_KV_F32>(a, grid, s);
     else if (kv->dtype == AB2_KV_BF16) rc = launch_split_hd<AB2_KV_BF16>(a, grid, s);
     else rc = launch_split_hd<AB2_KV_INT8>(a, grid, s);

@@ -1,6 +1,8 @@
 """KV cache semantics and grouped-query attention against the oracle.
 Attention tolerance: 1e-2 relative for bf16 / INT8-KV outputs (the bar stated
-for attention outputs), 1e-5 for f32 (summation order only)."""
+for attention outputs), 1e-5 for f32 (summation order only); an INT8 cache
+with f32 queries is held to 1e-3, because the tensor-core path rounds the
+queries and probabilities to fp16 before its MMAs."""
 import math
 
 import numpy as np
@@ -99,7 +101,7 @@ def _fill(cache, k, v, lens):
 
 
 @pytest.mark.parametrize("kv_dtype,act,tol", [("f32", torch.float32, 1e-5), ("bf16", torch.bfloat16, 1e-2),
-                                              ("int8", torch.bfloat16, 1e-2), ("int8", torch.float32, 1e-4)])
+                                              ("int8", torch.bfloat16, 1e-2), ("int8", torch.float32, 1e-3)])
 @pytest.mark.parametrize("h,kvh,hd,lens", [(32, 8, 128, [1000, 37]), (6, 2, 64, [160, 1, 33]),
                                            (8, 8, 128, [300]), (16, 2, 128, [2049, 512])])
 def test_decode_attention_matches_oracle(kv_dtype, act, tol, h, kvh, hd, lens):

@@ -47,8 +47,8 @@ def test_static_scratch_entry_point_matches_allocating_one(dtype, act):
 def test_static_scratch_rejects_oversized_problems():
     p = pkg()
     # Partials are indexed by the absolute cache row: rows 78..79 of an 80-row cache
-    # with 19 context splits need 80 * 32 * 19 * 130 = 6.3 M floats, more than the
-    # 2 Mi floats of the fixed array; rows 0..1 need 2 * 32 * 19 * 130 = 158 k.
+    # with 56 context splits need 80 * 32 * 56 * 130 = 18.6 M floats, more than the
+    # 2 Mi floats of the fixed array; rows 0..1 need 2 * 32 * 56 * 130 = 466 k.
     lens = [5000, 5000] + [8] * 76 + [5000, 5000]
     cache = _cache(p, lens, seed=42)
     q = torch.randn((2, 32, 128), device="cuda").to(torch.bfloat16)
