@@ -1,0 +1,179 @@
+#!/usr/bin/env python
+"""Micro-benchmarks of the three hot kernels on synthetic inputs of the
+benchmark specification's shapes.  Timing is with CUDA events on the launching
+stream after warm-up; weights / caches larger than L2 are cycled so every timed
+launch reads from HBM.
+
+    python aarambh-ai_b200/microbench.py gemv      [--m 1,4,16]      W4A16 dequant-GEMV (HBM GB/s)
+    python aarambh-ai_b200/microbench.py gemm      [--m 512,2048]    W4A16 tcgen05 GEMM (TFLOP/s)
+    python aarambh-ai_b200/microbench.py attention [--cases 8x16384] INT8-KV flash-decode (HBM GB/s)
+
+``--profile`` runs three launches of the first case only (for ncu captures).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import import_package  # noqa: E402
+
+SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 128256)]   # (K, N)
+
+
+def peak_hbm() -> float:
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        return 6650.0
+
+
+def peak_tflops() -> float:
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except (OSError, KeyError, ValueError):
+        return 1590.0
+
+
+def random_w4a16(pkg, N, K, seed):
+    """Uniform random packed ints, bf16 scales in [0.005, 0.02], zero points 0..15."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    qw = torch.randint(-2**31, 2**31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=g)
+    sc = (torch.rand(N, K // 128, device="cuda", generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    qz = torch.randint(-2**31, 2**31 - 1, (N, (K // 128 + 7) // 8), dtype=torch.int32, device="cuda", generator=g)
+    return pkg.QuantLinear.from_w4a16_gptq(qw, sc.view(torch.int16), qz, N, K, 128)
+
+
+def w4_bytes(N, K):
+    return K * N // 2 + (K // 128) * N * 2 + (K // 128) * N // 2
+
+
+def time_graph(fn, reps, stream):
+    """Captures `fn` in a CUDA graph and returns seconds per replay (launch overhead of the host excluded)."""
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            fn()
+        g.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            g.replay()
+        b.record(stream)
+        stream.synchronize()
+    return a.elapsed_time(b) * 1e-3 / reps
+
+
+def bench_gemv(pkg, args):
+    stream = torch.cuda.Stream()
+    for K, N in SHAPES:
+        copies = 1 if args.profile else max(2, math.ceil(400e6 / w4_bytes(N, K)))
+        lins = [random_w4a16(pkg, N, K, 2 + i) for i in range(copies)]
+        for M in args.m:
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            if args.profile:
+                for _ in range(3):
+                    lins[0](x)
+                torch.cuda.synchronize()
+                print("profiled case", K, N, M)
+                return
+            t = time_graph(lambda: [lin(x) for lin in lins], 5, stream) / copies
+            byt = w4_bytes(N, K) + 2 * M * (K + N)
+            print(json.dumps({"kernel": "gemv_w4a16_stream_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
+                              "GBs": round(byt / t / 1e9, 1), "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}),
+                  flush=True)
+        del lins
+
+
+def bench_gemm(pkg, args):
+    for K, N in SHAPES[:3]:
+        lin = random_w4a16(pkg, N, K, 2)
+        dense = lin.dequantise(torch.bfloat16)
+        for M in args.m:
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            for _ in range(3):
+                y = lin(x)
+            torch.cuda.synchronize()
+            if args.profile:
+                print("profiled case", K, N, M)
+                return
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                y = lin(x)
+            b.record()
+            torch.cuda.synchronize()
+            t = a.elapsed_time(b) * 1e-3 / 10
+            ref = x @ dense.T
+            err = ((y.float() - ref.float()).abs().max() / ref.float().abs().max()).item()
+            fl = 2.0 * M * K * N
+            print(json.dumps({"kernel": "gemm_w4a16_tc_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 1),
+                              "TFLOPs": round(fl / t / 1e12, 1), "frac_of_measured_bf16": round(fl / t / 1e12 / peak_tflops(), 3),
+                              "rel_err_vs_dense_bf16": err}), flush=True)
+
+
+def bench_attention(pkg, args):
+    h, kvh, hd = 32, 8, 128
+    for B, ctx in args.cases:
+        cache = pkg.KVCache(ctx, kvh, hd, h, batch=B, dtype="int8")
+        g = torch.Generator(device="cuda").manual_seed(3)
+        for b in range(B):
+            for s0 in range(0, ctx, 4096):
+                n = min(4096, ctx - s0)
+                k = torch.randn((1, n, kvh, hd), generator=g, device="cuda", dtype=torch.bfloat16)
+                cache.update(k, k, row0=b)
+        q = torch.randn((B, h, hd), generator=g, device="cuda").to(torch.bfloat16)
+        scale = 1 / math.sqrt(hd)
+        for _ in range(3):
+            pkg.dispatch.attention_decode(cache, q, scale)
+        torch.cuda.synchronize()
+        if args.profile:
+            print("profiled case", B, ctx)
+            return
+        reps = 20 if B * ctx < 1e6 else 8
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            pkg.dispatch.attention_decode(cache, q, scale)
+        b_.record()
+        torch.cuda.synchronize()
+        t = a.elapsed_time(b_) * 1e-3 / reps
+        byt = B * (ctx * (2 * kvh * hd + 2 * kvh * 4) + 2 * h * hd * 2)
+        print(json.dumps({"kernel": "attn_decode_mma_kernel", "B": B, "ctx": ctx, "us": round(t * 1e6, 1),
+                          "GBs": round(byt / t / 1e9, 1), "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}),
+              flush=True)
+        del cache
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemv", "gemm", "attention"])
+    ap.add_argument("--m", default=None)
+    ap.add_argument("--cases", default=None)
+    ap.add_argument("--profile", action="store_true")
+    args = ap.parse_args()
+    pkg = import_package()
+    torch.cuda.set_device(0)
+    if args.what == "gemv":
+        args.m = [int(v) for v in (args.m or "1,4,16").split(",")]
+        bench_gemv(pkg, args)
+    elif args.what == "gemm":
+        args.m = [int(v) for v in (args.m or "512,2048,8192").split(",")]
+        bench_gemm(pkg, args)
+    else:
+        default = "1x4096,1x16384,1x32768,8x4096,8x16384,8x32768,64x4096,64x16384,64x32768"
+        args.cases = [tuple(int(v) for v in c.split("x")) for c in (args.cases or default).split(",")]
+        bench_attention(pkg, args)
+    print(json.dumps({"device_status": pkg.device_status()}))
+
+
+if __name__ == "__main__":
+    main()
