@@ -159,9 +159,13 @@ def main():
     ap.add_argument("--m", default=None)
     ap.add_argument("--cases", default=None)
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--shape", default=None, help="K,N: restrict gemv / gemm to one weight shape")
     args = ap.parse_args()
     pkg = import_package()
     torch.cuda.set_device(0)
+    if args.shape:
+        k, n = (int(v) for v in args.shape.split(","))
+        SHAPES[:] = [(k, n)]
     if args.what == "gemv":
         args.m = [int(v) for v in (args.m or "1,4,16").split(",")]
         bench_gemv(pkg, args)
