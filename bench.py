@@ -57,8 +57,17 @@ def kv_bytes_per_token(c):
     return c["n_layers"] * (2 * c["n_kv_heads"] * c["head_dim"] + 2 * c["n_kv_heads"] * 4)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of gemv_w4a16_stream_kernel divided by its
+# algorithmic bytes, from one ncu capture on a 4096 x 128256 weight with one token
+# (profiles/gemv_w4a16_stream_kernel__k4096_n128256_m1.md).  The kernel streams every
+# weight block exactly once whatever the shape, so traffic grows in proportion to the bytes.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 283.07 / 279.4
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi.  The process is
+    started ahead of the warm-up (its start-up takes longer than a short timed
+    region); only rows that arrive between begin() and end() count."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -66,43 +75,59 @@ class ClockSampler:
 
     def __init__(self, gpu_index=0):
         self.rows, self.proc, self.gpu = [], None, gpu_index
-
-    def __enter__(self):
+        self.windows, self._t0 = [], None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
-        return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.monotonic(), [x.strip() for x in line.split(",")]))
+
+    def begin(self):
+        deadline = time.monotonic() + 5.0
+        while self.proc and not self.rows and time.monotonic() < deadline:
+            time.sleep(0.01)
+        self._t0 = time.monotonic()
+
+    def end(self):
+        self.windows.append((self._t0, time.monotonic() + 0.06))
+
+    def __enter__(self):
+        self.begin()
+        return self
 
     def __exit__(self, *exc):
+        self.end()
+
+    def close(self):
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(0.08)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+            self.proc = None
 
     def summary(self):
-        sm = sorted(int(r[1]) for r in self.rows if len(r) >= 9 and r[1].isdigit())
+        self.close()
+        rows = [r for t, r in self.rows if any(a <= t <= b for a, b in self.windows) and len(r) >= 9]
+        sm = sorted(int(r[1]) for r in rows if r[1].isdigit())
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
         reasons = set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            if len(r) >= 9:
-                for name, val in zip(names, r[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-        mx = [int(r[2]) for r in self.rows if len(r) >= 9 and r[2].isdigit()]
+        for r in rows:
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mx = [int(r[2]) for r in rows if r[2].isdigit()]
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
                 "samples": len(sm)}
 
@@ -261,13 +286,14 @@ def main():
             model.decode_step(bufs[step_no % 2], cache, None, bufs[(step_no + 1) % 2])
             step_no += 1
 
+        clocks = ClockSampler(local_rank)
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
         if world > 1:
             dist.barrier()
         a, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
+        with clocks:
             a.record(stream)
             for _ in range(args.steps):
                 step()
@@ -297,10 +323,11 @@ def main():
 
         for _ in range(3):
             host_step()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            host_step()
-        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        with clocks:
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                host_step()
+            e2e_s = (time.perf_counter() - t0) / e2e_steps
 
     local_cfg = dict(cfg, n_heads=cfg["n_heads"] // world, n_kv_heads=cfg["n_kv_heads"] // world,
                      ffn_hidden=cfg["ffn_hidden"] // world)
@@ -330,7 +357,10 @@ def main():
         "step_bytes": step_bytes,
         "step_hbm_frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, 4),
         "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_stream_kernel", "achieved": round(achieved, 1),
-                     "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": None,
+                     "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                     "traffic": round(gemv_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                     "traffic_source": "ncu dram read+write of this kernel on a 4096 x 128256 weight, one token "
+                                       "(283.07 MB for 279.4 MB algorithmic), scaled by the bytes one launch streams",
                      "peak_source": "measured" if peaks else "fallback",
                      "launches_per_step": gemv_launches, "bytes_per_launch": round(gemv_bytes)},
         "e2e": {"value": round(B / e2e_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * B,
