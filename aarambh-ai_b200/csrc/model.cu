@@ -21,6 +21,9 @@ using namespace ab2;
 namespace ab2 {
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s);
 int device_status_word(int **out);
+int w4a16_prepare_stream(cudaStream_t s);
+bool qlinear_w4a16_norm_fusable(const ab2_qweight *w, ab2_dtype dtype, int M);
+int qlinear_w4a16_norm(const ab2_qweight *w, const void *x, const float *norm_w, float eps, void *y, int epi, cudaStream_t s);
 bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype);
 int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s);
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
@@ -138,6 +141,19 @@ static int launch_rope_q(ab2_model *m, int T, int S, int row0, const int *base, 
         if (_rc != AB2_OK) return _rc; \
     } while (0)
 
+// out = epilogue(RMSNorm(x; norm_w) . W^T).  One decode token on the W4A16 fast path
+// normalises inside the GEMV; otherwise the norm is its own launch into m->xn.
+// epi: 0 plain projection (any format), 2 SwiGLU over an interleaved gate|up weight.
+static int norm_linear(ab2_model *m, const ab2_qweight *w, const void *x, const float *norm_w, int T, void *out,
+                       int epi, cudaStream_t s) {
+    const ab2_model_config &c = m->cfg;
+    if (m->fused_epilogues && qlinear_w4a16_norm_fusable(w, m->dtype, T))
+        return qlinear_w4a16_norm(w, x, norm_w, c.rms_eps, out, epi, s);
+    STEP(launch_rms_norm(x, norm_w, m->xn, T, c.d_model, c.rms_eps, m->dtype, s));
+    if (epi == 2) return qlinear_w4a16_mma_swiglu(w, m->xn, T, out, s);
+    return qlinear_dispatch(w, m->xn, T, m->dtype, out, s);
+}
+
 // The forward pass proper; every launch goes to `s`, nothing synchronises.
 static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S, int row0, int nrows,
                             const int *rope_base, int logits_mode, void *logits, uint32_t *argmax_out,
@@ -150,8 +166,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
     STEP(launch_embedding(m->embedding, ids, T, m->x, m->dtype, s));
     for (int l = 0; l < c.n_layers; ++l) {
         LayerWeights &L = m->layers[l];
-        STEP(launch_rms_norm(m->x, L.norm1, m->xn, T, d, c.rms_eps, m->dtype, s));
-        STEP(qlinear_dispatch(L.wqkv, m->xn, T, m->dtype, m->qkv, s));
+        STEP(norm_linear(m, L.wqkv, m->x, L.norm1, T, m->qkv, 0, s));
         if (S == 1) {
             // decode: RoPE, KV append, attention and split merge in one launch
             STEP(attention_decode_fused_device(kv, l, m->qkv, qkv_stride, m->attn, row0, nrows, scale, m->dtype,
@@ -176,8 +191,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
                 STEP(qlinear_w4a16_mma_f32(L.part[3], m->attn, T, m->proj32, s));
                 STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
                 add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
-                STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
-                STEP(qlinear_w4a16_mma_swiglu(L.wgu, m->xn, T, m->hid, s));
+                STEP(norm_linear(m, L.wgu, m->x, L.norm2, T, m->hid, 2, s));
                 STEP(qlinear_w4a16_mma_f32(L.part[6], m->hid, T, m->proj32, s));
                 STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
                 add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
@@ -208,8 +222,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
         } else if (m->fused_epilogues) {
             STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
-            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
-            STEP(qlinear_w4a16_mma_swiglu(L.wgu, m->xn, T, m->hid, s));
+            STEP(norm_linear(m, L.wgu, m->x, L.norm2, T, m->hid, 2, s));
             STEP(qlinear_w4a16_mma_add(L.part[6], m->hid, T, m->x, m->x, s));
         } else {
             STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
@@ -233,12 +246,11 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         hidden = m->proj;
         rows = nrows;
     }
-    STEP(launch_rms_norm(hidden, m->final_norm, m->xn, rows, d, c.rms_eps, m->dtype, s));
     void *lg = logits ? logits : m->gu;  // scratch when only the argmax is wanted
     if (m->tp && m->tp->world > 1) {
         // vocabulary-parallel LM head: local shard, all-gather, reorder to [rows][vocab]
         const int vn = c.vocab / m->tp->world;
-        STEP(qlinear_dispatch(m->lm_head, m->xn, rows, m->dtype, m->lg_local, s));
+        STEP(norm_linear(m, m->lm_head, hidden, m->final_norm, rows, m->lg_local, 0, s));
         void *gathered = rows == 1 ? lg : m->lg_all;
         STEP(tp_all_gather(m->tp, m->lg_local, gathered, (size_t)rows * vn, m->dtype, s));
         if (rows > 1) {
@@ -249,7 +261,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             AB2_LAUNCH_CHECK();
         }
     } else {
-        STEP(qlinear_dispatch(m->lm_head, m->xn, rows, m->dtype, lg, s));
+        STEP(norm_linear(m, m->lm_head, hidden, m->final_norm, rows, lg, 0, s));
     }
     if (argmax_out) {
         // last token of each row
@@ -487,6 +499,8 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         cudaGraph_t graph = nullptr;
+        rc = w4a16_prepare_stream(s);  // scratch of the GEMV is allocated outside the capture
+        if (rc != AB2_OK) return rc;
         AB2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         g_pdl_launch = m->fused_epilogues;  // every kernel of the fast path takes part in the chain
         rc = forward_launches(m, kv, ids_dev, 1, row0, nrows, kv->lens_dev, logits_dev ? 1 : 0, logits_dev, argmax_dev, kv->cap, s);

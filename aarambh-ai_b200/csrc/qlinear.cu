@@ -1,9 +1,14 @@
 // QatLinear::forward over packed weights: shape checks and kernel selection.
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "gemv_generic.cuh"
 #include "gemv_w4a16_mma.cuh"
+#include "gemv_w4a16_warp.cuh"
+#include "gemv_w4a16_m1.cuh"
 
 using namespace ab2;
 
@@ -97,14 +102,112 @@ bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype) {
     return w->fmt == FMT_W4A16 && w->group == 128 && dtype == AB2_BF16;
 }
 
+// Scratch of the warp-streaming GEMV (partial sums of tiles cut by a range
+// boundary, and one counter per tile), one set per (device, stream): launches
+// on one stream run in order and may share it, launches on different streams
+// may overlap and must not.  A set is allocated the first time its stream is
+// seen, which must not be while that stream is being captured: a caller that
+// captures graphs calls w4a16_prepare_stream() (or runs one eager launch) first.
+constexpr int W4W_MAX_TILES = 1 << 18;
+struct GemvScratch {
+    float *partials = nullptr;
+    int *counters = nullptr;
+    int max_ctas = 0;
+};
+static std::mutex g_scratch_mutex;
+static std::map<std::pair<int, cudaStream_t>, GemvScratch> g_scratch;
+
+static int gemv_scratch_for(cudaStream_t s, GemvScratch *out) {
+    int dev = 0;
+    AB2_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    auto key = std::make_pair(dev, s);
+    auto it = g_scratch.find(key);
+    if (it == g_scratch.end()) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return fail(AB2_ERR_UNSUPPORTED,
+                        "first quantised linear on this stream is inside a graph capture: run one launch "
+                        "on the stream before capturing (its scratch buffers are allocated then)");
+        GemvScratch sc;
+        sc.max_ctas = device_sm_count() * 4;
+        const size_t pbytes = (size_t)sc.max_ctas * W4W_WARPS * 2 * W4W_SLOT_FLOATS * sizeof(float);
+        AB2_CUDA(cudaMalloc((void **)&sc.partials, pbytes));
+        AB2_CUDA(cudaMalloc((void **)&sc.counters, W4W_MAX_TILES * sizeof(int)));
+        AB2_CUDA(cudaMemset(sc.counters, 0, W4W_MAX_TILES * sizeof(int)));
+        AB2_CUDA(cudaDeviceSynchronize());
+        it = g_scratch.emplace(key, sc).first;
+    }
+    *out = it->second;
+    return AB2_OK;
+}
+
+int w4a16_prepare_stream(cudaStream_t s) {
+    int *status = nullptr;
+    int rc = device_status_word(&status);
+    if (rc != AB2_OK) return rc;
+    GemvScratch sc;
+    return gemv_scratch_for(s, &sc);
+}
+
+// One token: activations prepared per CTA (gemv_w4a16_m1.cuh).  K bounds the
+// shared memory of a CTA, so very wide inputs stay on the general kernel.
+template <int EPI, int STAGES, int NV, bool NORM>
+static cudaError_t launch_w4a16_m1_inst(const ab2_qweight *w, const __nv_bfloat16 *x, const float *norm_w,
+                                        float eps, __nv_bfloat16 *y, const __nv_bfloat16 *resid, int grid,
+                                        const GemvScratch &sc, int *status, cudaStream_t s) {
+    const size_t smem = w4m1_smem_bytes<STAGES>(w->K);
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    return launch_kernel(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM>, dim3(grid), dim3(256), smem, s,
+                         (const uint32_t *)w->codes, x, norm_w, eps, y, resid, w->N, w->K, sc.partials,
+                         sc.counters, status);
+}
+
+template <int EPI>
+static cudaError_t launch_w4a16_m1(const ab2_qweight *w, const __nv_bfloat16 *x, const float *norm_w, float eps,
+                                   __nv_bfloat16 *y, const __nv_bfloat16 *resid, int grid, const GemvScratch &sc,
+                                   int *status, cudaStream_t s) {
+    if (w->K <= 8192) {
+        if (norm_w) return launch_w4a16_m1_inst<EPI, 5, 4, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+        return launch_w4a16_m1_inst<EPI, 5, 4, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+    }
+    if (norm_w) return launch_w4a16_m1_inst<EPI, 4, 8, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+    return launch_w4a16_m1_inst<EPI, 4, 8, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+}
+
+constexpr int W4M1_MAX_K = 16384;
+
 template <int EPI>
 static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void *y, const void *resid,
-                               cudaStream_t s) {
+                               cudaStream_t s, const float *norm_w = nullptr, float eps = 0.f) {
     int *status = nullptr;
     int rc = device_status_word(&status);
     if (rc != AB2_OK) return rc;
     const int tiles = (w->N + 15) / 16;
-    const int grid = std::min(tiles, device_sm_count() * 4);
+    static const char *which = getenv("AB2_GEMV_KERNEL");  // experiments: "cta" = shared-ring kernel
+    const bool cta_kernel = (which && which[0] == 'c') || tiles > W4W_MAX_TILES;
+    if (cta_kernel && norm_w) return fail(AB2_ERR_UNSUPPORTED, "the fused RMSNorm needs the warp-streaming GEMV");
+    GemvScratch sc;
+    int grid = std::min(tiles, device_sm_count() * 4);
+    if (!cta_kernel) {
+        rc = gemv_scratch_for(s, &sc);
+        if (rc != AB2_OK) return rc;
+        // at least eight blocks per warp (small weights are latency-bound: fewer, longer
+        // ranges keep most cut tiles inside one CTA); at most three resident CTAs per SM
+        static const int min_blocks = getenv("AB2_GEMV_MINB") ? std::max(1, atoi(getenv("AB2_GEMV_MINB"))) : 8;
+        const long long total = (long long)tiles * (w->K / 128);
+        static const int variant0 = getenv("AB2_GEMV_VARIANT") ? atoi(getenv("AB2_GEMV_VARIANT")) : 0;
+        const int cap = (variant0 >= 2 && M <= 8 && M > 1) ? sc.max_ctas : sc.max_ctas / 4 * 3;
+        grid = (int)std::min<long long>(cap, std::max<long long>(1, (total / min_blocks + W4W_WARPS - 1) / W4W_WARPS));
+    }
     const uint32_t *wt = (const uint32_t *)w->codes;
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     for (int m0 = 0; m0 < M; m0 += 16) {
@@ -114,8 +217,26 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
         const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
         int mv = M - m0 < 16 ? M - m0 : 16;
         cudaError_t e;
-        if (mv <= 8) e = launch_kernel(gemv_w4a16_stream_kernel<1, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
-        else e = launch_kernel(gemv_w4a16_stream_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
+        if (cta_kernel) {
+            if (mv <= 8) e = launch_kernel(gemv_w4a16_stream_kernel<1, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
+            else e = launch_kernel(gemv_w4a16_stream_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
+        } else {
+            static const int variant = getenv("AB2_GEMV_VARIANT") ? atoi(getenv("AB2_GEMV_VARIANT")) : 0;
+#define AB2_W4W_LAUNCH(NT_, OCC_, ZADD_)                                                                     \
+    launch_kernel(gemv_w4a16_warp_kernel<NT_, EPI, OCC_, ZADD_>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, \
+                  w->N, w->K, mv, sc.partials, sc.counters, status)
+            static const bool no_m1 = getenv("AB2_GEMV_NO_M1") != nullptr;
+            if (norm_w && !(M == 1 && w->K <= W4M1_MAX_K))
+                return fail(AB2_ERR_UNSUPPORTED, "the fused RMSNorm serves one token and K <= %d", W4M1_MAX_K);
+            if (mv == 1 && M == 1 && (norm_w || !no_m1) && w->K <= W4M1_MAX_K) {
+                e = launch_w4a16_m1<EPI>(w, xp, norm_w, eps, yp, rp, grid, sc, status, s);
+            } else if (mv > 8) e = AB2_W4W_LAUNCH(2, 3, true);
+            else if (variant == 1) e = AB2_W4W_LAUNCH(1, 3, false);
+            else if (variant == 2) e = AB2_W4W_LAUNCH(1, 4, true);
+            else if (variant == 3) e = AB2_W4W_LAUNCH(1, 4, false);
+            else e = AB2_W4W_LAUNCH(1, 3, true);
+#undef AB2_W4W_LAUNCH
+        }
         if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "GEMV launch failed: %s", cudaGetErrorString(e));
     }
     AB2_LAUNCH_CHECK();
@@ -136,6 +257,22 @@ int qlinear_w4a16_mma_f32(const ab2_qweight *w, const void *x, int M, float *y, 
 // y[M][N/2] = silu(gate) * up for a gate|up weight interleaved in 8-row halves
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
     return launch_w4a16_stream<W4_EPI_SWIGLU>(w, x, M, y, nullptr, s);
+}
+
+// One token with the RMSNorm of the input fused into the GEMV: y = epi(norm(x) . W^T).
+bool qlinear_w4a16_norm_fusable(const ab2_qweight *w, ab2_dtype dtype, int M) {
+    static const bool off = getenv("AB2_NO_NORM_FUSION") != nullptr;
+    return !off && qlinear_w4a16_mma_eligible(w, dtype) && M == 1 && w->K <= W4M1_MAX_K &&
+           (w->N + 15) / 16 <= W4W_MAX_TILES;
+}
+int qlinear_w4a16_norm(const ab2_qweight *w, const void *x, const float *norm_w, float eps, void *y, int epi,
+                       cudaStream_t s) {
+    switch (epi) {
+    case W4_EPI_STORE: return launch_w4a16_stream<W4_EPI_STORE>(w, x, 1, y, nullptr, s, norm_w, eps);
+    case W4_EPI_SWIGLU: return launch_w4a16_stream<W4_EPI_SWIGLU>(w, x, 1, y, nullptr, s, norm_w, eps);
+    case W4_EPI_F32: return launch_w4a16_stream<W4_EPI_F32>(w, x, 1, y, nullptr, s, norm_w, eps);
+    default: return fail(AB2_ERR_BAD_ARG, "unsupported epilogue %d for the fused RMSNorm", epi);
+    }
 }
 
 int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
