@@ -58,5 +58,11 @@ int attention_decode_mma_device(const ab2_kv *kv, int layer, const void *q, void
 int attention_decode_fused_device(ab2_kv *kv, int layer, const void *qkv, long long stride, void *out,
                                   int row0, int nrows, float scale, ab2_dtype dtype, const float *cos_t,
                                   const float *sin_t, const int *rope_pos, int len_hint, cudaStream_t s);
+// The same step for an INT8 cache with head_dim 128 and bf16 activations, one
+// thread-block cluster per (row, kv head); `max_len` bounds the context length.
+bool attention_decode_cluster_eligible(const ab2_kv *kv, ab2_dtype dtype, int max_len);
+int attention_decode_cluster_device(ab2_kv *kv, int layer, const void *qkv, long long stride, void *out,
+                                    int row0, int nrows, float scale, const float *cos_t, const float *sin_t,
+                                    const int *rope_pos, int max_len, cudaStream_t s);
 
 }  // namespace ab2

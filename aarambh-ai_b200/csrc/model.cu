@@ -169,9 +169,17 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         STEP(norm_linear(m, L.wqkv, m->x, L.norm1, T, m->qkv, 0, s));
         if (S == 1) {
             // decode: RoPE, KV append, attention and split merge in one launch
-            STEP(attention_decode_fused_device(kv, l, m->qkv, qkv_stride, m->attn, row0, nrows, scale, m->dtype,
-                                               m->cos_t, m->sin_t, rope_base == kv->lens_dev ? nullptr : rope_base,
-                                               len_hint, s));
+            int max_len = len_hint;
+            if (max_len <= 0)
+                for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + 1);
+            if (attention_decode_cluster_eligible(kv, m->dtype, max_len))
+                STEP(attention_decode_cluster_device(kv, l, m->qkv, qkv_stride, m->attn, row0, nrows, scale, m->cos_t,
+                                                     m->sin_t, rope_base == kv->lens_dev ? nullptr : rope_base,
+                                                     max_len, s));
+            else
+                STEP(attention_decode_fused_device(kv, l, m->qkv, qkv_stride, m->attn, row0, nrows, scale, m->dtype,
+                                                   m->cos_t, m->sin_t, rope_base == kv->lens_dev ? nullptr : rope_base,
+                                                   len_hint, s));
         } else {
             STEP(launch_rope_q(m, T, S, row0, rope_base, s));
             const char *kptr = (const char *)m->qkv + (size_t)c.n_heads * hd * esz;

@@ -228,7 +228,10 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
             static const bool no_m1 = getenv("AB2_GEMV_NO_M1") != nullptr;
             if (norm_w && !(M == 1 && w->K <= W4M1_MAX_K))
                 return fail(AB2_ERR_UNSUPPORTED, "the fused RMSNorm serves one token and K <= %d", W4M1_MAX_K);
-            if (mv == 1 && M == 1 && (norm_w || !no_m1) && w->K <= W4M1_MAX_K) {
+            // Without a norm to fuse, preparing K activations in every CTA pays only
+            // while K is small next to the rows a CTA streams.
+            static const int plain_max_k = getenv("AB2_M1_PLAIN_MAXK") ? atoi(getenv("AB2_M1_PLAIN_MAXK")) : 8192;
+            if (mv == 1 && M == 1 && (norm_w || (!no_m1 && w->K <= plain_max_k)) && w->K <= W4M1_MAX_K) {
                 e = launch_w4a16_m1<EPI>(w, xp, norm_w, eps, yp, rp, grid, sc, status, s);
             } else if (mv > 8) e = AB2_W4W_LAUNCH(2, 3, true);
             else if (variant == 1) e = AB2_W4W_LAUNCH(1, 3, false);

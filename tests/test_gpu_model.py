@@ -137,3 +137,37 @@ def test_fused_epilogue_path_matches_unfused_operators():
     x = x + packed["layers.0.w_down"](hid)
     ref = packed["embedding"](D.rms_norm(x, ones, 1e-5)).float()
     assert rel_err(got[0].cpu().numpy(), ref.cpu().numpy()) < 1e-2
+
+
+@pytest.mark.parametrize("prompt_len", [5, 150, 300, 600])
+def test_decode_step_head_dim_128_int8_kv_matches_oracle(prompt_len):
+    """The one-token step on the Large-class block shapes scaled down (head_dim
+    128, grouped queries, INT8 KV, W4A16 weights, bf16): graph-replayed decode
+    steps (cluster attention over 1, 2, 4 and 8 context splits, RMSNorm fused into
+    the one-token GEMV) against the dense f32 oracle run over the whole sequence,
+    and against the plain-launch decode of the same tokens."""
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
+               max_seq=1024)
+    gpu, cpu, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=640, capacity=640)
+    steps = 4
+    ids = prompt(cfg["vocab"], prompt_len + steps, 7)
+    ref = cpu.forward(ids[None], [0])[0]                       # [S, vocab]
+    cache = gpu.empty_kv_cache_with_capacity(prompt_len + steps + 2, dtype="int8")
+    cache2 = gpu.empty_kv_cache_with_capacity(prompt_len + steps + 2, dtype="int8")
+    gpu.forward_with_cache(ids[None, :prompt_len], 0, cache)
+    gpu.forward_with_cache(ids[None, :prompt_len], 0, cache2)
+    side = torch.cuda.Stream()
+    logits = torch.empty((1, cfg["vocab"]), dtype=torch.bfloat16, device="cuda")
+    tok = torch.empty(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for s in range(steps):
+        pos = prompt_len + s
+        with torch.cuda.stream(side):
+            tok.fill_(int(ids[pos]))
+            gpu.decode_step(tok, cache, logits, None)
+            side.synchronize()
+        got = logits.float().cpu().numpy()[0]
+        assert rel_err(got, ref[pos]) < 2e-2, (prompt_len, s)
+        plain = gpu.forward_decode_batch(np.array([[int(ids[pos])]]), [pos], cache2).float().cpu().numpy()[0, 0]
+        assert rel_err(got, plain) < 1e-2, (prompt_len, s)
+    assert pkg().device_status() == 0
