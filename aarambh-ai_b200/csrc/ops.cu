@@ -200,7 +200,30 @@ __global__ void argmax_kernel(const T *__restrict__ logits, int vocab, uint32_t 
     __shared__ long long warp_best[32];
     const T *row = logits + (size_t)blockIdx.x * vocab;
     long long best = LLONG_MIN;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = max(best, argmax_key(to_f32(row[i]), i));
+    if (sizeof(T) == 2 && ((uintptr_t)row & 15) == 0) {
+        // 16-bit logits: eight per load, every load of a thread in flight at once
+        const int nvec = vocab >> 3;
+        const uint4 *row4 = reinterpret_cast<const uint4 *>(row);
+        for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * blockDim.x) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x;
+                v[u] = i < nvec ? row4[i] : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i >= nvec) continue;
+                const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) best = max(best, argmax_key(to_f32(e[j]), i * 8 + j));
+            }
+        }
+        for (int i = (nvec << 3) + threadIdx.x; i < vocab; i += blockDim.x) best = max(best, argmax_key(to_f32(row[i]), i));
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = max(best, argmax_key(to_f32(row[i]), i));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
     if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = best;
@@ -231,7 +254,9 @@ __global__ void embedding_kernel(const uint32_t *__restrict__ ids, int vocab, in
                                  int N, int K, int group, T *out) {
     uint32_t id = ids[blockIdx.x];
     if (id >= (uint32_t)vocab) id = vocab - 1;  // ids are validated on the host; keep reads in range
-    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    // grid (tokens, slices of the row): one element per thread, so a row costs one
+    // round trip to memory instead of a chain of them
+    for (int k = blockIdx.y * blockDim.x + threadIdx.x; k < K; k += gridDim.y * blockDim.x) {
         size_t idx = (size_t)id * K + k;
         float v;
         if (fmt == FMT_I8) {
@@ -261,7 +286,8 @@ __global__ void embedding_kernel(const uint32_t *__restrict__ ids, int vocab, in
 
 int launch_embedding(const ab2_qweight *table, const uint32_t *ids, int tokens, void *out, ab2_dtype dtype,
                      cudaStream_t s) {
-#define AB2_EMB(T) embedding_kernel<T><<<tokens, 128, 0, s>>>(ids, table->N, table->fmt, table->codes, table->scales, table->zeros, table->block_params, table->N, table->K, table->group, (T *)out)
+    const dim3 grid(tokens, tokens <= 64 ? std::min(32, std::max(1, (table->K + 127) / 128)) : 1);
+#define AB2_EMB(T) embedding_kernel<T><<<grid, 128, 0, s>>>(ids, table->N, table->fmt, table->codes, table->scales, table->zeros, table->block_params, table->N, table->K, table->group, (T *)out)
     switch (dtype) {
     case AB2_F32: AB2_EMB(float); break;
     case AB2_F16: AB2_EMB(__half); break;

@@ -205,7 +205,8 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
         static const int min_blocks = getenv("AB2_GEMV_MINB") ? std::max(1, atoi(getenv("AB2_GEMV_MINB"))) : 8;
         const long long total = (long long)tiles * (w->K / 128);
         static const int variant0 = getenv("AB2_GEMV_VARIANT") ? atoi(getenv("AB2_GEMV_VARIANT")) : 0;
-        const int cap = (variant0 >= 2 && M <= 8 && M > 1) ? sc.max_ctas : sc.max_ctas / 4 * 3;
+        static const int occ = getenv("AB2_GEMV_OCC") ? std::max(1, std::min(3, atoi(getenv("AB2_GEMV_OCC")))) : 3;
+        const int cap = (variant0 >= 2 && M <= 8 && M > 1) ? sc.max_ctas : sc.max_ctas / 4 * occ;
         grid = (int)std::min<long long>(cap, std::max<long long>(1, (total / min_blocks + W4W_WARPS - 1) / W4W_WARPS));
     }
     const uint32_t *wt = (const uint32_t *)w->codes;
