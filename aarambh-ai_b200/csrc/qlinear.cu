@@ -162,7 +162,7 @@ static cudaError_t launch_w4a16_m1_inst(const ab2_qweight *w, const __nv_bfloat1
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 74 * 1024);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }

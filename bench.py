@@ -343,8 +343,9 @@ def main():
     ctx_mid = PROMPT + max(args.warmup, 3) + args.steps // 2
     # per GPU: a rank reads its 1/world share of the layer weights, head and KV
     step_bytes = (step_weight_bytes(cfg) + B * ctx_mid * kv_bytes_per_token(cfg)) // world
-    # embedding, per layer {norm, qkv, attention, o, norm, gate|up+SwiGLU, down}, final norm, head, argmax, commit
-    launches_per_step = 1 + cfg["n_layers"] * (7 if world == 1 else 11) + 3 + 1
+    # embedding, per layer {norm+qkv, attention, o, norm+gate|up+SwiGLU, down} (tensor parallel: plus the two
+    # f32 residual adds after the all-reduces), norm+head, argmax, commit; NCCL's kernels are not counted
+    launches_per_step = (1 + cfg["n_layers"] * (5 if world == 1 else 7) + 3) if B == 1 else None
 
     line = {
         "metric": "INT4 decode tok/s", "value": round(B * 1e3 / ms_per_step, 2), "unit": "tokens/s",
@@ -356,7 +357,7 @@ def main():
                    "l2": "weights (3.7 GB per step) exceed the 126 MB L2"},
         "step_bytes": step_bytes,
         "step_hbm_frac": round(step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, 4),
-        "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_stream_kernel", "achieved": round(achieved, 1),
+        "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_m1_kernel (gemv_w4a16_warp_kernel where K > 8192)", "achieved": round(achieved, 1),
                      "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                      "traffic": round(gemv_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
                      "traffic_source": "ncu dram read+write of this kernel on a 4096 x 128256 weight, one token "
@@ -365,7 +366,7 @@ def main():
                      "launches_per_step": gemv_launches, "bytes_per_launch": round(gemv_bytes)},
         "e2e": {"value": round(B / e2e_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 4 * B},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": (launches_per_step if launches_per_step else 1 + cfg["n_layers"] * 7 + 4) * args.steps,
         "clocks": clocks.summary(),
         "device_status": status,
     }
