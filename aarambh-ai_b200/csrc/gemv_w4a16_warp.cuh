@@ -12,8 +12,8 @@
 // Arithmetic per block is that of gemv_w4a16_mma.cuh: nibbles become bf16 with
 // one shift and one LOP3 per pair (0x4300 | q == 128 + q exactly) and feed
 // mma.sync.m16n8k16 (bf16 x bf16 -> f32) with the 16 weight rows as A and up to
-// 8 tokens as B; the zero point rides a second MMA chain (1..8 tokens) or an
-// exact bf16x2 add (9..16 tokens); the bf16 scale is applied per group in f32.
+// 8 tokens as B; the zero point leaves by an exact bf16x2 add on the A registers;
+// the bf16 scale is applied per group in f32.
 //
 // A tile whose groups all lie inside one warp's range is finished by that warp.
 // A tile cut by a range boundary is finished by whichever of its contributors
@@ -127,15 +127,11 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
 // partials: [gridDim.x * 8 warps][2][W4W_SLOT_FLOATS] floats; counters: one int
 // per 16-row tile, zero on entry and on exit.
 //
-// ZADD selects how the zero point is applied: by an exact bf16x2 add on the A
-// registers, (128 + q) - (128 + z), or (false, up to 8 tokens only) by a second
-// MMA chain whose A operand is the constant -(128 + z).
-template <int NT, int EPI, int OCC = 3, bool ZADD = true>
-__global__ void __launch_bounds__(256, OCC)
+template <int NT, int EPI>
+__global__ void __launch_bounds__(256, 3)
 gemv_w4a16_warp_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__restrict__ x,
                        __nv_bfloat16 *y, const __nv_bfloat16 *resid, int N, int K, int M,
                        float *partials, int *counters, int *status) {
-    static_assert(ZADD || NT == 1, "the zero-point MMA chain serves up to 8 tokens");
     __shared__ alignas(128) uint32_t ring[W4W_WARPS][W4W_STAGES][W4_BLOCK_WORDS];
     __shared__ alignas(8) uint64_t full_bar[W4W_WARPS][W4W_STAGES];
     constexpr uint32_t BLOCK_BYTES = W4_BLOCK_WORDS * 4;
@@ -232,33 +228,21 @@ gemv_w4a16_warp_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__r
                     a[2 * jj] = w4_pair_bf16(words_a[wi], jj, k_mask, k_magic);
                     a[2 * jj + 1] = w4_pair_bf16(words_b[wi], jj, k_mask, k_magic);
                 }
-                if (ZADD) {
+                // the zero point leaves by an exact bf16x2 add: (128 + q) - (128 + z)
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        a[2 * jj] = bf16x2_add(a[2 * jj], nza);
-                        a[2 * jj + 1] = bf16x2_add(a[2 * jj + 1], nzb);
-                    }
+                for (int jj = 0; jj < 4; ++jj) {
+                    a[2 * jj] = bf16x2_add(a[2 * jj], nza);
+                    a[2 * jj + 1] = bf16x2_add(a[2 * jj + 1], nzb);
                 }
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
-                    // two independent accumulation chains (even / odd k-steps, or
-                    // codes / zero point)
+                    // two independent accumulation chains (even / odd k-steps)
                     if (wi == 0) {
                         mma_bf16_16816_init(d[t], a[0], a[1], a[2], a[3], xw[t][wi].x, xw[t][wi].y);
-                        if (!ZADD)
-                            mma_bf16_16816_init(dz[t], nza, nzb, nza, nzb, xw[t][wi].x, xw[t][wi].y);
-                        else
-                            mma_bf16_16816_init(dz[t], a[4], a[5], a[6], a[7], xw[t][wi].z, xw[t][wi].w);
+                        mma_bf16_16816_init(dz[t], a[4], a[5], a[6], a[7], xw[t][wi].z, xw[t][wi].w);
                     } else {
                         mma_bf16_16816(d[t], a[0], a[1], a[2], a[3], xw[t][wi].x, xw[t][wi].y);
-                        if (!ZADD)
-                            mma_bf16_16816(dz[t], nza, nzb, nza, nzb, xw[t][wi].x, xw[t][wi].y);
-                        else
-                            mma_bf16_16816(dz[t], a[4], a[5], a[6], a[7], xw[t][wi].z, xw[t][wi].w);
-                    }
-                    if (!ZADD) {
-                        mma_bf16_16816(d[t], a[4], a[5], a[6], a[7], xw[t][wi].z, xw[t][wi].w);
-                        mma_bf16_16816(dz[t], nza, nzb, nza, nzb, xw[t][wi].z, xw[t][wi].w);
+                        mma_bf16_16816(dz[t], a[4], a[5], a[6], a[7], xw[t][wi].z, xw[t][wi].w);
                     }
                 }
             }

@@ -130,7 +130,7 @@ static int gemv_scratch_for(cudaStream_t s, GemvScratch *out) {
                         "first quantised linear on this stream is inside a graph capture: run one launch "
                         "on the stream before capturing (its scratch buffers are allocated then)");
         GemvScratch sc;
-        sc.max_ctas = device_sm_count() * 4;
+        sc.max_ctas = device_sm_count() * 3;
         const size_t pbytes = (size_t)sc.max_ctas * W4W_WARPS * 2 * W4W_SLOT_FLOATS * sizeof(float);
         AB2_CUDA(cudaMalloc((void **)&sc.partials, pbytes));
         AB2_CUDA(cudaMalloc((void **)&sc.counters, W4W_MAX_TILES * sizeof(int)));
@@ -184,6 +184,7 @@ static cudaError_t launch_w4a16_m1(const ab2_qweight *w, const __nv_bfloat16 *x,
 }
 
 constexpr int W4M1_MAX_K = 16384;
+constexpr int W4M1_PLAIN_MAX_K = 8192;
 
 template <int EPI>
 static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void *y, const void *resid,
@@ -192,23 +193,16 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     int rc = device_status_word(&status);
     if (rc != AB2_OK) return rc;
     const int tiles = (w->N + 15) / 16;
-    static const char *which = getenv("AB2_GEMV_KERNEL");  // experiments: "cta" = shared-ring kernel
-    const bool cta_kernel = (which && which[0] == 'c') || tiles > W4W_MAX_TILES;
-    if (cta_kernel && norm_w) return fail(AB2_ERR_UNSUPPORTED, "the fused RMSNorm needs the warp-streaming GEMV");
+    AB2_REQUIRE(tiles <= W4W_MAX_TILES, AB2_ERR_UNSUPPORTED, "out_features=%d exceeds the %d rows the decode GEMV serves",
+                w->N, W4W_MAX_TILES * 16);
     GemvScratch sc;
-    int grid = std::min(tiles, device_sm_count() * 4);
-    if (!cta_kernel) {
-        rc = gemv_scratch_for(s, &sc);
-        if (rc != AB2_OK) return rc;
-        // at least eight blocks per warp (small weights are latency-bound: fewer, longer
-        // ranges keep most cut tiles inside one CTA); at most three resident CTAs per SM
-        static const int min_blocks = getenv("AB2_GEMV_MINB") ? std::max(1, atoi(getenv("AB2_GEMV_MINB"))) : 8;
-        const long long total = (long long)tiles * (w->K / 128);
-        static const int variant0 = getenv("AB2_GEMV_VARIANT") ? atoi(getenv("AB2_GEMV_VARIANT")) : 0;
-        static const int occ = getenv("AB2_GEMV_OCC") ? std::max(1, std::min(3, atoi(getenv("AB2_GEMV_OCC")))) : 3;
-        const int cap = (variant0 >= 2 && M <= 8 && M > 1) ? sc.max_ctas : sc.max_ctas / 4 * occ;
-        grid = (int)std::min<long long>(cap, std::max<long long>(1, (total / min_blocks + W4W_WARPS - 1) / W4W_WARPS));
-    }
+    rc = gemv_scratch_for(s, &sc);
+    if (rc != AB2_OK) return rc;
+    // Three resident CTAs per SM at most, and at least eight blocks per warp: small
+    // weights are latency-bound, and fewer, longer ranges keep most cut tiles inside
+    // one CTA (finished through shared memory).
+    const long long total = (long long)tiles * (w->K / 128);
+    const int grid = (int)std::min<long long>(sc.max_ctas, std::max<long long>(1, (total / 8 + W4W_WARPS - 1) / W4W_WARPS));
     const uint32_t *wt = (const uint32_t *)w->codes;
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     for (int m0 = 0; m0 < M; m0 += 16) {
@@ -218,29 +212,18 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
         const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
         int mv = M - m0 < 16 ? M - m0 : 16;
         cudaError_t e;
-        if (cta_kernel) {
-            if (mv <= 8) e = launch_kernel(gemv_w4a16_stream_kernel<1, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
-            else e = launch_kernel(gemv_w4a16_stream_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N, w->K, mv, status);
-        } else {
-            static const int variant = getenv("AB2_GEMV_VARIANT") ? atoi(getenv("AB2_GEMV_VARIANT")) : 0;
-#define AB2_W4W_LAUNCH(NT_, OCC_, ZADD_)                                                                     \
-    launch_kernel(gemv_w4a16_warp_kernel<NT_, EPI, OCC_, ZADD_>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, \
-                  w->N, w->K, mv, sc.partials, sc.counters, status)
-            static const bool no_m1 = getenv("AB2_GEMV_NO_M1") != nullptr;
-            if (norm_w && !(M == 1 && w->K <= W4M1_MAX_K))
-                return fail(AB2_ERR_UNSUPPORTED, "the fused RMSNorm serves one token and K <= %d", W4M1_MAX_K);
-            // Without a norm to fuse, preparing K activations in every CTA pays only
-            // while K is small next to the rows a CTA streams.
-            static const int plain_max_k = getenv("AB2_M1_PLAIN_MAXK") ? atoi(getenv("AB2_M1_PLAIN_MAXK")) : 8192;
-            if (mv == 1 && M == 1 && (norm_w || (!no_m1 && w->K <= plain_max_k)) && w->K <= W4M1_MAX_K) {
-                e = launch_w4a16_m1<EPI>(w, xp, norm_w, eps, yp, rp, grid, sc, status, s);
-            } else if (mv > 8) e = AB2_W4W_LAUNCH(2, 3, true);
-            else if (variant == 1) e = AB2_W4W_LAUNCH(1, 3, false);
-            else if (variant == 2) e = AB2_W4W_LAUNCH(1, 4, true);
-            else if (variant == 3) e = AB2_W4W_LAUNCH(1, 4, false);
-            else e = AB2_W4W_LAUNCH(1, 3, true);
-#undef AB2_W4W_LAUNCH
-        }
+        if (norm_w && !(M == 1 && w->K <= W4M1_MAX_K))
+            return fail(AB2_ERR_UNSUPPORTED, "the fused RMSNorm serves one token and K <= %d", W4M1_MAX_K);
+        // One token: the kernel that prepares the activations per CTA, while K is small
+        // next to the rows a CTA streams (or there is a norm to fuse); else the general one.
+        if (M == 1 && (norm_w || w->K <= W4M1_PLAIN_MAX_K) && w->K <= W4M1_MAX_K)
+            e = launch_w4a16_m1<EPI>(w, xp, norm_w, eps, yp, rp, grid, sc, status, s);
+        else if (mv > 8)
+            e = launch_kernel(gemv_w4a16_warp_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N,
+                              w->K, mv, sc.partials, sc.counters, status);
+        else
+            e = launch_kernel(gemv_w4a16_warp_kernel<1, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N,
+                              w->K, mv, sc.partials, sc.counters, status);
         if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "GEMV launch failed: %s", cudaGetErrorString(e));
     }
     AB2_LAUNCH_CHECK();

@@ -7,6 +7,9 @@ launch reads from HBM.
     python aarambh-ai_b200/microbench.py gemv      [--m 1,4,16]      W4A16 dequant-GEMV (HBM GB/s)
     python aarambh-ai_b200/microbench.py gemm      [--m 512,2048]    W4A16 tcgen05 GEMM (TFLOP/s)
     python aarambh-ai_b200/microbench.py attention [--cases 8x16384] INT8-KV flash-decode (HBM GB/s)
+    python aarambh-ai_b200/microbench.py step      [--layers 2] [--ctx 512] one-token decoder step of a short
+                                                   Large-shaped stack (a few hundred MB on the device: the
+                                                   case to capture the step's kernels under a profiler)
 
 ``--profile`` runs three launches of the first case only (for ncu captures).
 """
@@ -87,7 +90,7 @@ def bench_gemv(pkg, args):
                 return
             t = time_graph(lambda: [lin(x) for lin in lins], 5, stream) / copies
             byt = w4_bytes(N, K) + 2 * M * (K + N)
-            print(json.dumps({"kernel": "gemv_w4a16_stream_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
+            print(json.dumps({"kernel": "gemv_w4a16_m1_kernel" if M == 1 else "gemv_w4a16_warp_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
                               "GBs": round(byt / t / 1e9, 1), "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}),
                   flush=True)
         del lins
@@ -153,9 +156,62 @@ def bench_attention(pkg, args):
         del cache
 
 
+def bench_step(pkg, args):
+    """Decode steps of an n-layer stack with the Large block shapes (d 4096, 32 / 8 heads of 128, hidden 14336,
+    vocab 32000; W4A16 g128, INT8 KV, bf16), context `ctx`.  Prints the step time; with --profile runs 4 steps."""
+    L, d, h, kvh, hd, ffn, vocab = args.layers, 4096, 32, 8, 128, 14336, 32000
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    weights = {}
+
+    def make(name, n, k):
+        w = torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        weights[name] = pkg.QuantLinear.quantise(w, "w4a16", 128)
+
+    for l in range(L):
+        for nm, (n, k) in {"wq": (h * hd, d), "wk": (kvh * hd, d), "wv": (kvh * hd, d), "wo": (d, h * hd),
+                           "w_gate": (ffn, d), "w_up": (ffn, d), "w_down": (d, ffn)}.items():
+            make(f"layers.{l}.{nm}", n, k)
+        weights[f"layers.{l}.norm1"] = torch.ones(d, device="cuda")
+        weights[f"layers.{l}.norm2"] = torch.ones(d, device="cuda")
+    weights["final_norm"] = torch.ones(d, device="cuda")
+    make("embedding", vocab, d)
+    make("lm_head", vocab, d)
+    cfg = pkg.ModelConfig(L, d, h, kvh, hd, ffn, vocab, args.ctx + 64, 1e-5, 10000.0, False)
+    model = pkg.AarambhModel(cfg, weights, dtype=torch.bfloat16, max_tokens=args.ctx)
+    cache = model.empty_kv_cache_with_capacity(args.ctx + 48, batch=1, dtype="int8")
+    prompt = torch.randint(0, vocab, (1, args.ctx), generator=torch.Generator().manual_seed(1))
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        logits = model.forward_with_cache(prompt, 0, cache, row=0, last_only=True)
+        bufs = [pkg.dispatch.argmax(logits.view(1, -1)).clone(), torch.empty(1, dtype=torch.int32, device="cuda")]
+        n = 0
+
+        def step():
+            nonlocal n
+            model.decode_step(bufs[n % 2], cache, None, bufs[(n + 1) % 2])
+            n += 1
+
+        for _ in range(4):
+            step()
+        stream.synchronize()
+        if args.profile:
+            print("profiled case", L, args.ctx)
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(32):
+            step()
+        b.record(stream)
+        stream.synchronize()
+    print(json.dumps({"workload": f"decode step, {L} Large-shaped layers, context {args.ctx}",
+                      "us_per_step": round(a.elapsed_time(b) * 1e3 / 32, 2)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm", "attention"])
+    ap.add_argument("what", choices=["gemv", "gemm", "attention", "step"])
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--m", default=None)
     ap.add_argument("--cases", default=None)
     ap.add_argument("--profile", action="store_true")
@@ -172,6 +228,8 @@ def main():
     elif args.what == "gemm":
         args.m = [int(v) for v in (args.m or "512,2048,8192").split(",")]
         bench_gemm(pkg, args)
+    elif args.what == "step":
+        bench_step(pkg, args)
     else:
         default = "1x4096,1x16384,1x32768,8x4096,8x16384,8x32768,64x4096,64x16384,64x32768"
         args.cases = [tuple(int(v) for v in c.split("x")) for c in (args.cases or default).split(",")]
