@@ -57,11 +57,11 @@ def kv_bytes_per_token(c):
     return c["n_layers"] * (2 * c["n_kv_heads"] * c["head_dim"] + 2 * c["n_kv_heads"] * 4)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of gemv_w4a16_stream_kernel divided by its
+# dram__bytes_read.sum + dram__bytes_write.sum of gemv_w4a16_m1_kernel divided by its
 # algorithmic bytes, from one ncu capture on a 4096 x 128256 weight with one token
-# (profiles/gemv_w4a16_stream_kernel__k4096_n128256_m1.md).  The kernel streams every
+# (profiles/gemv_w4a16_m1_kernel__k4096_n128256_m1.md).  The kernel streams every
 # weight block exactly once whatever the shape, so traffic grows in proportion to the bytes.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 283.07 / 279.4
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 283.18 / 279.4
 
 
 class ClockSampler:
@@ -361,7 +361,7 @@ def main():
                      "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                      "traffic": round(gemv_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
                      "traffic_source": "ncu dram read+write of this kernel on a 4096 x 128256 weight, one token "
-                                       "(283.07 MB for 279.4 MB algorithmic), scaled by the bytes one launch streams",
+                                       "(283.18 MB for 279.4 MB algorithmic), scaled by the bytes one launch streams",
                      "peak_source": "measured" if peaks else "fallback",
                      "launches_per_step": gemv_launches, "bytes_per_launch": round(gemv_bytes)},
         "e2e": {"value": round(B / e2e_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * B,
