@@ -95,6 +95,8 @@ SIGNATURES = {
     "ab2_tp_create": ([_pp, _i, _i, _p], _i),
     "ab2_tp_destroy": ([_p], _i),
     "ab2_tp_all_reduce": ([_p, _p, C.c_size_t, _i, _p], _i),
+    "ab2_tp_peer_export": ([_p, C.c_size_t, _p], _i),
+    "ab2_tp_peer_attach": ([_p, _p], _i),
     "ab2_model_rope_tables": ([_p, _pp, _pp], _i),
     "ab2_model_forward": ([_p, _p, _p, _i, _i, _i, _p, _i, _p, _p, _p], _i),
     "ab2_model_decode_step": ([_p, _p, _p, _i, _i, _p, _p, _p], _i),

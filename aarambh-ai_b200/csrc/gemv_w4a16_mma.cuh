@@ -99,7 +99,9 @@ constexpr int W4_BLOCK_WORDS = 272;      // 16 rows x 16 code words + 16 paramet
 // alias `y`), silu(gate) * up for a weight whose 16-row tiles hold 8 gate rows
 // followed by the 8 matching up rows (W4_EPI_SWIGLU; y is [M][N/2]), or the f32
 // sums ([M][N] floats at `y`, W4_EPI_F32): the partial result of a row-parallel
-// shard, summed across ranks before it is rounded.
-enum { W4_EPI_STORE = 0, W4_EPI_ADD = 1, W4_EPI_SWIGLU = 2, W4_EPI_F32 = 3 };
+// shard, summed across ranks before it is rounded.  W4_EPI_F32_PEER stores the
+// same sums into every rank's inbox of the tensor-parallel peer exchange (`y`
+// then points to the ab2_tp_peer_desc in device memory).
+enum { W4_EPI_STORE = 0, W4_EPI_ADD = 1, W4_EPI_SWIGLU = 2, W4_EPI_F32 = 3, W4_EPI_F32_PEER = 4 };
 
 }  // namespace ab2

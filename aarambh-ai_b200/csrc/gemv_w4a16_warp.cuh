@@ -27,6 +27,7 @@
 #pragma once
 
 #include "gemv_w4a16_mma.cuh"
+#include "tp.cuh"
 
 namespace ab2 {
 
@@ -39,6 +40,15 @@ template <int NT, int EPI>
 __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int tile, int r, int c,
                                                __nv_bfloat16 *y, const __nv_bfloat16 *resid, int N,
                                                int M) {
+    // peer exchange: buffer (epoch + 1) & 1, slot of this rank, in every rank's inbox
+    const ab2_tp_peer_desc *peers = nullptr;
+    size_t peer_off = 0;
+    int peer_world = 0;
+    if (EPI == W4_EPI_F32_PEER) {
+        peers = reinterpret_cast<const ab2_tp_peer_desc *>(y);
+        peer_world = peers->world;
+        peer_off = ((size_t)((*peers->epoch + 1) & 1u) * peer_world + peers->rank) * peers->max_elems;
+    }
 #pragma unroll
     for (int t = 0; t < NT; ++t)
 #pragma unroll
@@ -63,6 +73,8 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
                     const size_t o = (size_t)tok * N + row;
                     if (EPI == W4_EPI_F32) {  // unrounded partial sum of a row-parallel shard
                         reinterpret_cast<float *>(y)[o] = v;
+                    } else if (EPI == W4_EPI_F32_PEER) {  // the same, stored over NVLink with every rank
+                        for (int p = 0; p < peer_world; ++p) peers->inbox[p][peer_off + o] = v;
                     } else {
                         if (EPI == W4_EPI_ADD)  // residual + bf16(projection), as residual + x does
                             v = __bfloat162float(resid[o]) + __bfloat162float(__float2bfloat16_rn(v));

@@ -28,6 +28,7 @@ bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype);
 int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s);
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 int qlinear_w4a16_mma_f32(const ab2_qweight *w, const void *x, int M, float *y, cudaStream_t s);
+int qlinear_w4a16_mma_f32_peer(const ab2_qweight *w, const void *x, int M, ab2_tp *tp, cudaStream_t s);
 }
 extern "C" int ab2_qweight_interleave_gate_up(ab2_qweight **out, const ab2_qweight *gate, const ab2_qweight *up);
 
@@ -196,13 +197,26 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             // row-parallel O and down produce partial sums: all-reduce, then the residual add
             const size_t nd = (size_t)T * d;
             if (m->fused_epilogues) {
-                STEP(qlinear_w4a16_mma_f32(L.part[3], m->attn, T, m->proj32, s));
-                STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
-                add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
+                // f32 partial sums meet either in the ranks' inboxes over NVLink (the projection
+                // stores them there; one small kernel per exchange) or through NCCL
+                const bool peer = T <= 16 && tp_peer_ready(m->tp, nd);
+                if (peer) {
+                    STEP(qlinear_w4a16_mma_f32_peer(L.part[3], m->attn, T, m->tp, s));
+                    STEP(tp_peer_reduce_add(m->tp, m->x, nd, s));
+                } else {
+                    STEP(qlinear_w4a16_mma_f32(L.part[3], m->attn, T, m->proj32, s));
+                    STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
+                    add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
+                }
                 STEP(norm_linear(m, L.wgu, m->x, L.norm2, T, m->hid, 2, s));
-                STEP(qlinear_w4a16_mma_f32(L.part[6], m->hid, T, m->proj32, s));
-                STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
-                add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
+                if (peer) {
+                    STEP(qlinear_w4a16_mma_f32_peer(L.part[6], m->hid, T, m->tp, s));
+                    STEP(tp_peer_reduce_add(m->tp, m->x, nd, s));
+                } else {
+                    STEP(qlinear_w4a16_mma_f32(L.part[6], m->hid, T, m->proj32, s));
+                    STEP(tp_all_reduce(m->tp, m->proj32, nd, AB2_F32, s));
+                    add_f32_projection_kernel<<<(unsigned)ceil_div(nd, 256), 256, 0, s>>>((__nv_bfloat16 *)m->x, m->proj32, nd);
+                }
                 AB2_LAUNCH_CHECK();
             } else {
                 STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));

@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "gemv_generic.cuh"
+#include "tp.cuh"
 #include "gemv_w4a16_mma.cuh"
 #include "gemv_w4a16_warp.cuh"
 #include "gemv_w4a16_m1.cuh"
@@ -207,8 +208,9 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     for (int m0 = 0; m0 < M; m0 += 16) {
         const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;
-        __nv_bfloat16 *yp = EPI == W4_EPI_F32 ? (__nv_bfloat16 *)((float *)y + (size_t)m0 * out_n)
-                                              : (__nv_bfloat16 *)y + (size_t)m0 * out_n;
+        __nv_bfloat16 *yp = EPI == W4_EPI_F32_PEER ? (__nv_bfloat16 *)y  // descriptor of the peer exchange (one pass)
+                            : EPI == W4_EPI_F32  ? (__nv_bfloat16 *)((float *)y + (size_t)m0 * out_n)
+                                                 : (__nv_bfloat16 *)y + (size_t)m0 * out_n;
         const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
         int mv = M - m0 < 16 ? M - m0 : 16;
         cudaError_t e;
@@ -240,6 +242,12 @@ int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, c
 // y[M][N] f32 = x . W^T, unrounded (partial sums of a row-parallel shard)
 int qlinear_w4a16_mma_f32(const ab2_qweight *w, const void *x, int M, float *y, cudaStream_t s) {
     return launch_w4a16_stream<W4_EPI_F32>(w, x, M, y, nullptr, s);
+}
+// the same partial sums stored into every rank's inbox of the peer exchange
+int qlinear_w4a16_mma_f32_peer(const ab2_qweight *w, const void *x, int M, ab2_tp *tp, cudaStream_t s) {
+    AB2_REQUIRE(M <= 16 && tp_peer_ready(tp, (size_t)M * w->N), AB2_ERR_BAD_ARG,
+                "the peer exchange cannot take %d x %d sums", M, w->N);
+    return launch_w4a16_stream<W4_EPI_F32_PEER>(w, x, M, (void *)tp->desc_dev, nullptr, s);
 }
 // y[M][N/2] = silu(gate) * up for a gate|up weight interleaved in 8-row halves
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {

@@ -7,6 +7,16 @@
 //
 // NCCL is resolved at run time from the library the host process already
 // loaded (libnccl.so.2), so the shared object has no link-time dependency on it.
+//
+// The all-reduce of the decoder's row-parallel projections does not have to go
+// through NCCL: once the ranks have exchanged CUDA IPC handles
+// (ab2_tp_peer_export / ab2_tp_peer_attach), the projection kernel stores its f32
+// partial sums straight into every rank's inbox over NVLink, and one small
+// kernel per exchange signals the peers, waits (bounded) for their signals,
+// adds the partials in rank order and applies the residual.  Inboxes are
+// double-buffered by the parity of a per-rank exchange count kept in device
+// memory, so graph replays need no host-side sequence number.  Only plain
+// stores and loads touch peer memory.
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -65,6 +75,76 @@ ncclDataType_t nccl_type(ab2_dtype d) {
 
 namespace ab2 {
 
+int device_status_word(int **out);
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One CTA.  The partial sums of exchange e = epoch + 1 sit in buffer e & 1 of
+// every inbox (stored there by the projection kernels that ran before this one
+// on each rank).  x += bf16(sum_r partial_r), summed in rank order on every rank.
+__global__ void __launch_bounds__(1024)
+tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc *desc, int *status) {
+    __shared__ int failed;
+    pdl_wait();  // this rank's partial sums (and x) come from the preceding kernels
+    pdl_launch_dependents();
+    const ab2_tp_peer_desc d = *desc;
+    const uint32_t e = *d.epoch + 1;
+    if (threadIdx.x == 0) failed = 0;
+    __syncthreads();
+    if ((int)threadIdx.x < d.world && (int)threadIdx.x != d.rank) {
+        const int p = threadIdx.x;
+        __threadfence_system();
+        st_release_sys(d.flags[p] + d.rank, e);  // "my partial sums of exchange e are in your inbox"
+        const uint32_t *mine = d.flags[d.rank] + p;
+        bool ok = false;
+        for (int spin = 0; spin < (1 << 24); ++spin) {
+            // the count only grows; a peer that is ahead has already passed e
+            if ((int32_t)(ld_acquire_sys(mine) - e) >= 0) { ok = true; break; }
+            __nanosleep(20);
+        }
+        if (!ok) failed = 1;
+    }
+    __syncthreads();
+    if (failed) {
+        if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+        return;
+    }
+    const float *box = d.inbox[d.rank] + (size_t)(e & 1u) * d.world * d.max_elems;
+    for (size_t i = threadIdx.x; i < count; i += blockDim.x) {
+        float sum = 0.f;
+        for (int r = 0; r < d.world; ++r) sum += __ldcg(box + (size_t)r * d.max_elems + i);
+        x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(__float2bfloat16_rn(sum)));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *d.epoch = e;
+}
+
+}  // namespace
+
+bool tp_peer_ready(const ab2_tp *tp, size_t count) {
+    return tp && tp->world > 1 && tp->attached && count <= tp->max_elems;
+}
+
+int tp_peer_reduce_add(ab2_tp *tp, void *x_bf16, size_t count, cudaStream_t s) {
+    AB2_REQUIRE(tp_peer_ready(tp, count), AB2_ERR_BAD_ARG, "the peer exchange is not attached or %zu elements exceed it", count);
+    int *status = nullptr;
+    int rc = device_status_word(&status);
+    if (rc != AB2_OK) return rc;
+    cudaError_t e = launch_kernel(tp_peer_reduce_add_kernel, dim3(1), dim3(1024), 0, s, (__nv_bfloat16 *)x_bf16, count,
+                                  (const ab2_tp_peer_desc *)tp->desc_dev, status);
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "peer reduce launch failed: %s", cudaGetErrorString(e));
+    return AB2_OK;
+}
+
 int tp_all_reduce(ab2_tp *tp, void *buf, size_t count, ab2_dtype dtype, cudaStream_t s) {
     if (!tp || tp->world == 1) return AB2_OK;
     AB2_NCCL(g_nccl.AllReduce(buf, buf, count, nccl_type(dtype), ncclSum, (ncclComm_t)tp->comm, s));
@@ -95,6 +175,8 @@ AB2_API int ab2_tp_create(ab2_tp **out, int rank, int world, const void *id128) 
     AB2_REQUIRE(world >= 1 && rank >= 0 && rank < world, AB2_ERR_BAD_ARG, "rank %d outside world size %d", rank, world);
     ab2_tp *tp = new ab2_tp();
     tp->rank = rank; tp->world = world; tp->comm = nullptr;
+    tp->local_block = nullptr; tp->desc_dev = nullptr; tp->max_elems = 0; tp->attached = false;
+    for (int i = 0; i < AB2_TP_MAX_WORLD; ++i) tp->peer_block[i] = nullptr;
     if (world > 1) {
         AB2_REQUIRE(id128 != nullptr, AB2_ERR_BAD_ARG, "a unique id is needed for more than one rank");
         int rc = load_nccl();
@@ -116,6 +198,10 @@ AB2_API int ab2_tp_create(ab2_tp **out, int rank, int world, const void *id128) 
 AB2_API int ab2_tp_destroy(ab2_tp *tp) {
     if (!tp) return AB2_OK;
     if (tp->comm) g_nccl.CommDestroy((ncclComm_t)tp->comm);
+    for (int i = 0; i < AB2_TP_MAX_WORLD; ++i)
+        if (tp->peer_block[i]) cudaIpcCloseMemHandle(tp->peer_block[i]);
+    if (tp->desc_dev) cudaFree(tp->desc_dev);
+    if (tp->local_block) cudaFree(tp->local_block);
     delete tp;
     return AB2_OK;
 }
@@ -123,4 +209,52 @@ AB2_API int ab2_tp_destroy(ab2_tp *tp) {
 AB2_API int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype dtype, ab2_stream stream) {
     AB2_REQUIRE(tp && buf_dev, AB2_ERR_BAD_ARG, "null argument");
     return tp_all_reduce(tp, buf_dev, count, dtype, (cudaStream_t)stream);
+}
+
+// Layout of a rank's block: inbox [2][world][max_elems] f32, then flags [world] u32, then the epoch word.
+static size_t peer_block_bytes(int world, size_t max_elems) {
+    return 2 * (size_t)world * max_elems * sizeof(float) + ((size_t)world + 1) * sizeof(uint32_t) + 256;
+}
+
+AB2_API int ab2_tp_peer_export(ab2_tp *tp, size_t max_elems, void *handle64_host) {
+    AB2_REQUIRE(tp && handle64_host, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(tp->world > 1 && tp->world <= AB2_TP_MAX_WORLD, AB2_ERR_UNSUPPORTED,
+                "the peer exchange serves 2..%d ranks, got %d", AB2_TP_MAX_WORLD, tp->world);
+    AB2_REQUIRE(max_elems > 0 && max_elems % 4 == 0, AB2_ERR_BAD_SHAPE, "max_elems must be a positive multiple of 4");
+    AB2_REQUIRE(tp->local_block == nullptr, AB2_ERR_BAD_ARG, "the peer exchange was exported already");
+    const size_t bytes = peer_block_bytes(tp->world, max_elems);
+    AB2_CUDA(cudaMalloc(&tp->local_block, bytes));
+    AB2_CUDA(cudaMemset(tp->local_block, 0, bytes));
+    AB2_CUDA(cudaDeviceSynchronize());
+    tp->max_elems = max_elems;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle is 64 bytes");
+    cudaIpcMemHandle_t h;
+    AB2_CUDA(cudaIpcGetMemHandle(&h, tp->local_block));
+    memcpy(handle64_host, &h, 64);
+    return AB2_OK;
+}
+
+AB2_API int ab2_tp_peer_attach(ab2_tp *tp, const void *handles_host) {
+    AB2_REQUIRE(tp && handles_host, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(tp->local_block != nullptr && !tp->attached, AB2_ERR_BAD_ARG, "export the local block first (once)");
+    ab2_tp_peer_desc d;
+    memset(&d, 0, sizeof(d));
+    const size_t inbox_floats = 2 * (size_t)tp->world * tp->max_elems;
+    for (int p = 0; p < tp->world; ++p) {
+        void *base = tp->local_block;
+        if (p != tp->rank) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const char *)handles_host + (size_t)p * 64, 64);
+            AB2_CUDA(cudaIpcOpenMemHandle(&tp->peer_block[p], h, cudaIpcMemLazyEnablePeerAccess));
+            base = tp->peer_block[p];
+        }
+        d.inbox[p] = (float *)base;
+        d.flags[p] = (uint32_t *)((float *)base + inbox_floats);
+    }
+    d.epoch = d.flags[tp->rank] + tp->world;
+    d.rank = tp->rank; d.world = tp->world; d.max_elems = tp->max_elems;
+    AB2_CUDA(cudaMalloc((void **)&tp->desc_dev, sizeof(d)));
+    AB2_CUDA(cudaMemcpy(tp->desc_dev, &d, sizeof(d), cudaMemcpyHostToDevice));
+    tp->attached = true;
+    return AB2_OK;
 }

@@ -15,6 +15,7 @@ which part of every weight a rank owns:
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import replace
 
 import torch
@@ -82,15 +83,31 @@ class TensorParallel:
         return buf.raw
 
     @classmethod
-    def from_torch_distributed(cls):
-        """Rank 0 makes the id; it is broadcast over the default process group."""
+    def from_torch_distributed(cls, peer_exchange: bool = True, max_elems: int = 16 * 8192):
+        """Rank 0 makes the id; it is broadcast over the default process group.  With
+        `peer_exchange` the ranks also swap CUDA IPC handles so that the decoder's
+        partial sums travel over NVLink peer memory instead of NCCL (up to
+        `max_elems` sums per exchange: 16 tokens of d_model 8192 by default)."""
         import torch.distributed as dist
         rank, world = dist.get_rank(), dist.get_world_size()
         if world == 1:
             return cls(0, 1, None)
         ids = [cls.new_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
-        return cls(rank, world, ids[0])
+        tp = cls(rank, world, ids[0])
+        if peer_exchange and world <= 8 and os.environ.get("AB2_TP_NCCL_ONLY") is None:
+            tp.attach_peers(max_elems)
+        return tp
+
+    def attach_peers(self, max_elems: int) -> None:
+        """Exports this rank's inbox, gathers every rank's handle, attaches."""
+        import torch.distributed as dist
+        buf = C.create_string_buffer(64)
+        check(lib.ab2_tp_peer_export(self._h, max_elems, buf))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, buf.raw)
+        check(lib.ab2_tp_peer_attach(self._h, C.create_string_buffer(b"".join(handles), 64 * self.world)))
+        dist.barrier()
 
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         from .qlinear import dtype_code, stream_ptr

@@ -298,6 +298,21 @@ int ab2_tp_create(ab2_tp **out, int rank, int world, const void *id128_host);
 int ab2_tp_destroy(ab2_tp *tp);
 /* In-place sum over ranks of `count` elements (NCCL all-reduce). */
 int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype dtype, ab2_stream stream);
+/* One-shot exchange of the decoder's f32 partial sums over NVLink peer memory
+ * instead of NCCL (no counterpart in the reference, whose only collective is the
+ * NCCL all-reduce above).  Every rank calls ab2_tp_peer_export (allocates its
+ * inbox for up to max_elems sums per rank and writes a 64-byte CUDA IPC handle
+ * to handle64_host), the caller gathers the handles of all ranks in rank order
+ * (world x 64 bytes, the same channel that carried the unique id), and every
+ * rank calls ab2_tp_peer_attach with them.  From then on a decoder whose step has
+ * at most 16 tokens and tokens x d_model <= max_elems lets the row-parallel
+ * projections store their sums into every rank's inbox and meets the other
+ * ranks in one small kernel per exchange (bounded wait; AB2_ERR_TIMEOUT in the
+ * device status word when a peer does not arrive).  The ranks must be processes
+ * on GPUs of one box with peer access; every rank must run the same sequence of
+ * steps.  Attach before the first step is captured. */
+int ab2_tp_peer_export(ab2_tp *tp, size_t max_elems, void *handle64_host);
+int ab2_tp_peer_attach(ab2_tp *tp, const void *handles_host);
 int ab2_model_set_tp(ab2_model *m, ab2_tp *tp);
 /* AarambhModel::forward_with_cache (model.rs:508-587; nrows = 1, S = prompt
  * length) and forward_decode_batch (model.rs:590-641; S = 1): ids_dev

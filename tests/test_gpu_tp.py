@@ -1,6 +1,7 @@
 """Tensor-parallel decoder against the single-GPU decoder (needs 2 GPUs; skipped
-otherwise): same seeded weights, sharded over 2 NCCL ranks, logits within 1e-2
-relative and the same greedy tokens."""
+otherwise): same seeded weights, sharded over 2 ranks, logits within 1e-2
+relative and the same greedy tokens - once with the partial sums exchanged over
+NVLink peer memory, once through NCCL; plain launches and graph-replayed steps."""
 import os
 import socket
 
@@ -55,10 +56,23 @@ def _run(model, steps=6):
         lg = model.forward_decode_batch(torch.tensor([[toks[-1]]]), [5 + i], cache).float().cpu().numpy().ravel()
         logits.append(lg)
         toks.append(int(np.argmax(lg)))
+    # the graph-replayed step on a side stream
+    side = torch.cuda.Stream()
+    out = torch.empty((1, CFG["vocab"]), dtype=torch.bfloat16, device="cuda")
+    tok = torch.empty(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for i in range(steps):
+        with torch.cuda.stream(side):
+            tok.fill_(toks[-1])
+            model.decode_step(tok, cache, out, None)
+            side.synchronize()
+        lg = out.float().cpu().numpy().ravel()
+        logits.append(lg)
+        toks.append(int(np.argmax(lg)))
     return np.stack(logits), toks
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, peer):
     import torch.distributed as dist
     import sys
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -68,12 +82,12 @@ def _worker(rank, world, port, out):
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         pkg = import_package()
-        tp = pkg.TensorParallel.from_torch_distributed()
+        tp = pkg.TensorParallel.from_torch_distributed(peer_exchange=peer)
         logits, toks = _run(_build(pkg, rank, world, tp))
         if rank == 0:
             ref_logits, ref_toks = _run(_build(pkg, 0, 1, None))
             err = float(np.abs(logits - ref_logits).max() / np.abs(ref_logits).max())
-            out.put(("result", err, toks, ref_toks))
+            out.put(("result", err, toks, ref_toks, pkg.device_status()))
         dist.barrier()
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001
@@ -81,17 +95,19 @@ def _worker(rank, world, port, out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_matches_single_gpu():
+@pytest.mark.parametrize("peer", [True, False])
+def test_tp2_matches_single_gpu(peer):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out, peer)) for r in range(2)]
     for p in procs:
         p.start()
     msg = out.get(timeout=300)
     for p in procs:
         p.join(timeout=120)
     assert msg[0] == "result", msg
-    _, err, toks, ref_toks = msg
+    _, err, toks, ref_toks, status = msg
+    assert status == 0
     assert err < 1e-2, err
     assert toks == ref_toks
