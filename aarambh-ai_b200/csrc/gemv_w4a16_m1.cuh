@@ -79,12 +79,21 @@ constexpr int W4M1_LOCAL_TILES = 64;  // cut tiles a CTA can finish through shar
 // norm_w, rounded to bf16 as the stand-alone kernel does), so the normalisation
 // costs no launch of its own.  NV = vectors of 8 activations a thread keeps in
 // registers between the two passes of the prologue (K <= 2048 * NV).
-template <int EPI, int STAGES, int NV, bool NORM>
+//
+// PEER_IN (tensor parallel, with NORM): the input is the residual stream plus
+// the sum over ranks of the partial sums waiting in this rank's inbox of the
+// peer exchange (tp.cuh).  CTA 0 tells the peers that this rank's partial sums
+// are in place, every CTA waits (bounded) for the peers' signals, adds the
+// partials in rank order and rounds as the stand-alone reduce does; CTA 0 also
+// writes the new residual stream to `x_out` (not `x`: other CTAs still read it),
+// and the CTA that finishes its prologue last advances the exchange count.
+template <int EPI, int STAGES, int NV, bool NORM, bool PEER_IN = false>
 __global__ void __launch_bounds__(256, 3)
 gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__restrict__ x,
                      const float *__restrict__ norm_w, float eps, __nv_bfloat16 *y,
                      const __nv_bfloat16 *resid, int N, int K, float *partials, int *counters,
-                     int *status) {
+                     int *status, const ab2_tp_peer_desc *peers = nullptr, __nv_bfloat16 *x_out = nullptr) {
+    static_assert(!PEER_IN || NORM, "the peer exchange is consumed by the normalising kernels");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float2 warp_part[W4W_WARPS];                 // (sum of squares, largest magnitude)
     __shared__ float2 cta_part[W4W_WARPS][2][8];            // partial sums of cut tiles, rows (r, r + 8)
@@ -131,6 +140,59 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     pdl_wait();
     pdl_launch_dependents();
 
+    // ---- tensor parallel: meet the other ranks -------------------------------
+    const float *box = nullptr;
+    size_t box_stride = 0;
+    int box_world = 0;
+    uint32_t exchange = 0;
+    if (PEER_IN) {
+        __shared__ int peer_failed;
+        const ab2_tp_peer_desc d = *peers;
+        exchange = *d.epoch + 1;
+        if (threadIdx.x == 0) peer_failed = 0;
+        __syncthreads();
+        // CTA 0 talks to the peers (system scope, over NVLink); the other CTAs wait for its
+        // word in local memory instead of all polling the peers' flags
+        if (blockIdx.x == 0) {
+            if ((int)threadIdx.x < d.world && (int)threadIdx.x != d.rank) {
+                const int p = threadIdx.x;
+                __threadfence_system();
+                asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(d.flags[p] + d.rank), "r"(exchange) : "memory");
+                const uint32_t *mine = d.flags[d.rank] + p;
+                bool ok = false;
+                for (int spin = 0; spin < (1 << 24); ++spin) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(mine) : "memory");
+                    if ((int32_t)(v - exchange) >= 0) { ok = true; break; }
+                    __nanosleep(20);
+                }
+                if (!ok) peer_failed = 1;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0 && !peer_failed)
+                asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(d.ready), "r"(exchange) : "memory");
+        } else {
+            if (threadIdx.x == 0) {
+                bool ok = false;
+                for (int spin = 0; spin < (1 << 24); ++spin) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(d.ready) : "memory");
+                    if ((int32_t)(v - exchange) >= 0) { ok = true; break; }
+                    __nanosleep(20);
+                }
+                if (!ok) peer_failed = 1;
+            }
+            __syncthreads();
+        }
+        if (peer_failed) {
+            if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+            return;
+        }
+        box = d.inbox[d.rank] + (size_t)(exchange & 1u) * d.world * d.max_elems;
+        box_stride = d.max_elems;
+        box_world = d.world;
+    }
+
     // ---- prologue, pass 1: sum of squares and largest magnitude ---------------
     const uint4 *x4 = reinterpret_cast<const uint4 *>(x);
     const int nvec = K >> 3;
@@ -140,6 +202,26 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     for (int it = 0; it < NV; ++it) {
         const int i = threadIdx.x + it * 256;
         xv[it] = i < nvec ? __ldcg(x4 + i) : make_uint4(0u, 0u, 0u, 0u);
+        if (PEER_IN && i < nvec) {
+            // residual + bf16(sum over ranks), element by element as the stand-alone reduce does
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int rk = 0; rk < box_world; ++rk) {
+                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)rk * box_stride) + 2 * i);
+                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)rk * box_stride) + 2 * i + 1);
+                sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
+                sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+            }
+            uint32_t w[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float f0 = __uint_as_float(w[j] << 16) + __bfloat162float(__float2bfloat16_rn(sum[2 * j]));
+                const float f1 = __uint_as_float(w[j] & 0xffff0000u) + __bfloat162float(__float2bfloat16_rn(sum[2 * j + 1]));
+                w[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f0)) |
+                       ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f1)) << 16);
+            }
+            xv[it] = make_uint4(w[0], w[1], w[2], w[3]);
+            if (blockIdx.x == 0) reinterpret_cast<uint4 *>(x_out)[i] = xv[it];
+        }
         const uint32_t w[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
         float nw[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
         if (NORM && i < nvec) {
@@ -236,6 +318,15 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
         }
     }
     __syncthreads();
+    if (PEER_IN && threadIdx.x == 0) {
+        // every CTA has read the exchange count and its inbox: the last one closes the exchange
+        const ab2_tp_peer_desc d = *peers;
+        if (atomicAdd(d.done, 1u) == gridDim.x - 1) {
+            *d.done = 0;
+            __threadfence();
+            *d.epoch = exchange;
+        }
+    }
     if (nblk == 0) return;
 
     // Opaque register copies of the constants of the nibble extraction.

@@ -24,6 +24,8 @@ int device_status_word(int **out);
 int w4a16_prepare_stream(cudaStream_t s);
 bool qlinear_w4a16_norm_fusable(const ab2_qweight *w, ab2_dtype dtype, int M);
 int qlinear_w4a16_norm(const ab2_qweight *w, const void *x, const float *norm_w, float eps, void *y, int epi, cudaStream_t s);
+int qlinear_w4a16_norm_peer(const ab2_qweight *w, const void *x, const float *norm_w, float eps, void *y, int epi,
+                            ab2_tp *tp, void *x_out, cudaStream_t s);
 bool qlinear_w4a16_mma_eligible(const ab2_qweight *w, ab2_dtype dtype);
 int qlinear_w4a16_mma_add(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, cudaStream_t s);
 int qlinear_w4a16_mma_swiglu(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
@@ -165,9 +167,25 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
     const long long qkv_stride = (long long)(c.n_heads + 2 * c.n_kv_heads) * hd;
     const float scale = (float)(1.0 / std::sqrt((double)hd));
     STEP(launch_embedding(m->embedding, ids, T, m->x, m->dtype, s));
+    // Tensor parallel, one token: the partial sums of a row-parallel projection stay in the
+    // ranks' inboxes ("pending") and the next normalising GEMV adds them to the residual
+    // stream in its prologue, writing the new stream to the other of two buffers.
+    void *xcur = m->x;
+    bool pending = false;
+    const bool fuse_exchange = m->tp && m->tp->world > 1 && m->fused_epilogues && T == 1 &&
+                               tp_peer_ready(m->tp, (size_t)d) && qlinear_w4a16_norm_fusable(m->layers[0].wqkv, m->dtype, T) &&
+                               getenv("AB2_TP_SEPARATE_REDUCE") == nullptr;
+    auto consume = [&](const ab2_qweight *w, const float *norm_w, void *out, int epi) -> int {
+        void *xnext = xcur == m->x ? m->xn : m->x;
+        int rc2 = qlinear_w4a16_norm_peer(w, xcur, norm_w, c.rms_eps, out, epi, m->tp, xnext, s);
+        xcur = xnext;
+        pending = false;
+        return rc2;
+    };
     for (int l = 0; l < c.n_layers; ++l) {
         LayerWeights &L = m->layers[l];
-        STEP(norm_linear(m, L.wqkv, m->x, L.norm1, T, m->qkv, 0, s));
+        if (pending) STEP(consume(L.wqkv, L.norm1, m->qkv, 0));
+        else STEP(norm_linear(m, L.wqkv, xcur, L.norm1, T, m->qkv, 0, s));
         if (S == 1) {
             // decode: RoPE, KV append, attention and split merge in one launch
             int max_len = len_hint;
@@ -200,6 +218,13 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
                 // f32 partial sums meet either in the ranks' inboxes over NVLink (the projection
                 // stores them there; one small kernel per exchange) or through NCCL
                 const bool peer = T <= 16 && tp_peer_ready(m->tp, nd);
+                if (fuse_exchange) {
+                    STEP(qlinear_w4a16_mma_f32_peer(L.part[3], m->attn, T, m->tp, s));
+                    STEP(consume(L.wgu, L.norm2, m->hid, 2));
+                    STEP(qlinear_w4a16_mma_f32_peer(L.part[6], m->hid, T, m->tp, s));
+                    pending = true;
+                    continue;
+                }
                 if (peer) {
                     STEP(qlinear_w4a16_mma_f32_peer(L.part[3], m->attn, T, m->tp, s));
                     STEP(tp_peer_reduce_add(m->tp, m->x, nd, s));
@@ -257,7 +282,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         }
     }
     if (logits_mode == 0 && argmax_out == nullptr) return AB2_OK;
-    const void *hidden = m->x;
+    const void *hidden = xcur;
     int rows = T;
     if (logits_mode != 2 && S > 1) {  // only the last token of each row is needed
         switch (m->dtype) {
@@ -272,7 +297,8 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
     if (m->tp && m->tp->world > 1) {
         // vocabulary-parallel LM head: local shard, all-gather, reorder to [rows][vocab]
         const int vn = c.vocab / m->tp->world;
-        STEP(norm_linear(m, m->lm_head, hidden, m->final_norm, rows, m->lg_local, 0, s));
+        if (pending) STEP(consume(m->lm_head, m->final_norm, m->lg_local, 0));
+        else STEP(norm_linear(m, m->lm_head, hidden, m->final_norm, rows, m->lg_local, 0, s));
         void *gathered = rows == 1 ? lg : m->lg_all;
         STEP(tp_all_gather(m->tp, m->lg_local, gathered, (size_t)rows * vn, m->dtype, s));
         if (rows > 1) {

@@ -153,29 +153,40 @@ int w4a16_prepare_stream(cudaStream_t s) {
 
 // One token: activations prepared per CTA (gemv_w4a16_m1.cuh).  K bounds the
 // shared memory of a CTA, so very wide inputs stay on the general kernel.
-template <int EPI, int STAGES, int NV, bool NORM>
+template <int EPI, int STAGES, int NV, bool NORM, bool PEER_IN = false>
 static cudaError_t launch_w4a16_m1_inst(const ab2_qweight *w, const __nv_bfloat16 *x, const float *norm_w,
                                         float eps, __nv_bfloat16 *y, const __nv_bfloat16 *resid, int grid,
-                                        const GemvScratch &sc, int *status, cudaStream_t s) {
+                                        const GemvScratch &sc, int *status, cudaStream_t s,
+                                        const ab2_tp_peer_desc *peers = nullptr, __nv_bfloat16 *x_out = nullptr) {
     const size_t smem = w4m1_smem_bytes<STAGES>(w->K);
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM>,
+        cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM, PEER_IN>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 74 * 1024);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    return launch_kernel(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM>, dim3(grid), dim3(256), smem, s,
+    return launch_kernel(gemv_w4a16_m1_kernel<EPI, STAGES, NV, NORM, PEER_IN>, dim3(grid), dim3(256), smem, s,
                          (const uint32_t *)w->codes, x, norm_w, eps, y, resid, w->N, w->K, sc.partials,
-                         sc.counters, status);
+                         sc.counters, status, peers, x_out);
 }
 
 template <int EPI>
 static cudaError_t launch_w4a16_m1(const ab2_qweight *w, const __nv_bfloat16 *x, const float *norm_w, float eps,
                                    __nv_bfloat16 *y, const __nv_bfloat16 *resid, int grid, const GemvScratch &sc,
-                                   int *status, cudaStream_t s) {
+                                   int *status, cudaStream_t s, const ab2_tp_peer_desc *peers = nullptr,
+                                   __nv_bfloat16 *x_out = nullptr) {
+    if (peers) {  // tensor parallel: the input is the residual plus the exchanged partial sums (norm fused)
+        if constexpr (EPI == W4_EPI_STORE || EPI == W4_EPI_SWIGLU) {
+            if (w->K <= 8192)
+                return launch_w4a16_m1_inst<EPI, 5, 4, true, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s, peers, x_out);
+            return launch_w4a16_m1_inst<EPI, 4, 8, true, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s, peers, x_out);
+        } else {
+            return cudaErrorInvalidValue;
+        }
+    }
     if (w->K <= 8192) {
         if (norm_w) return launch_w4a16_m1_inst<EPI, 5, 4, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
         return launch_w4a16_m1_inst<EPI, 5, 4, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
@@ -189,7 +200,8 @@ constexpr int W4M1_PLAIN_MAX_K = 8192;
 
 template <int EPI>
 static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void *y, const void *resid,
-                               cudaStream_t s, const float *norm_w = nullptr, float eps = 0.f) {
+                               cudaStream_t s, const float *norm_w = nullptr, float eps = 0.f,
+                               const ab2_tp_peer_desc *peers = nullptr, void *x_out = nullptr) {
     int *status = nullptr;
     int rc = device_status_word(&status);
     if (rc != AB2_OK) return rc;
@@ -219,7 +231,7 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
         // One token: the kernel that prepares the activations per CTA, while K is small
         // next to the rows a CTA streams (or there is a norm to fuse); else the general one.
         if (M == 1 && (norm_w || w->K <= W4M1_PLAIN_MAX_K) && w->K <= W4M1_MAX_K)
-            e = launch_w4a16_m1<EPI>(w, xp, norm_w, eps, yp, rp, grid, sc, status, s);
+            e = launch_w4a16_m1<EPI>(w, xp, norm_w, eps, yp, rp, grid, sc, status, s, peers, (__nv_bfloat16 *)x_out);
         else if (mv > 8)
             e = launch_kernel(gemv_w4a16_warp_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xp, yp, rp, w->N,
                               w->K, mv, sc.partials, sc.counters, status);
@@ -267,6 +279,20 @@ int qlinear_w4a16_norm(const ab2_qweight *w, const void *x, const float *norm_w,
     case W4_EPI_SWIGLU: return launch_w4a16_stream<W4_EPI_SWIGLU>(w, x, 1, y, nullptr, s, norm_w, eps);
     case W4_EPI_F32: return launch_w4a16_stream<W4_EPI_F32>(w, x, 1, y, nullptr, s, norm_w, eps);
     default: return fail(AB2_ERR_BAD_ARG, "unsupported epilogue %d for the fused RMSNorm", epi);
+    }
+}
+
+// The same with the tensor-parallel exchange consumed in the prologue: the input is
+// x + bf16(sum over ranks of the partial sums in the inbox); the new residual stream is
+// written to x_out (a buffer other than x).
+int qlinear_w4a16_norm_peer(const ab2_qweight *w, const void *x, const float *norm_w, float eps, void *y, int epi,
+                            ab2_tp *tp, void *x_out, cudaStream_t s) {
+    AB2_REQUIRE(tp_peer_ready(tp, (size_t)w->K) && x_out && x_out != x, AB2_ERR_BAD_ARG,
+                "the peer exchange is not attached, too small, or x_out aliases x");
+    switch (epi) {
+    case W4_EPI_STORE: return launch_w4a16_stream<W4_EPI_STORE>(w, x, 1, y, nullptr, s, norm_w, eps, tp->desc_dev, x_out);
+    case W4_EPI_SWIGLU: return launch_w4a16_stream<W4_EPI_SWIGLU>(w, x, 1, y, nullptr, s, norm_w, eps, tp->desc_dev, x_out);
+    default: return fail(AB2_ERR_BAD_ARG, "unsupported epilogue %d for the fused exchange", epi);
     }
 }
 

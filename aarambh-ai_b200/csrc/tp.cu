@@ -211,9 +211,9 @@ AB2_API int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype
     return tp_all_reduce(tp, buf_dev, count, dtype, (cudaStream_t)stream);
 }
 
-// Layout of a rank's block: inbox [2][world][max_elems] f32, then flags [world] u32, then the epoch word.
+// Layout of a rank's block: inbox [2][world][max_elems] f32, then flags [world] u32, the epoch, done and ready words.
 static size_t peer_block_bytes(int world, size_t max_elems) {
-    return 2 * (size_t)world * max_elems * sizeof(float) + ((size_t)world + 1) * sizeof(uint32_t) + 256;
+    return 2 * (size_t)world * max_elems * sizeof(float) + ((size_t)world + 3) * sizeof(uint32_t) + 256;
 }
 
 AB2_API int ab2_tp_peer_export(ab2_tp *tp, size_t max_elems, void *handle64_host) {
@@ -252,6 +252,8 @@ AB2_API int ab2_tp_peer_attach(ab2_tp *tp, const void *handles_host) {
         d.flags[p] = (uint32_t *)((float *)base + inbox_floats);
     }
     d.epoch = d.flags[tp->rank] + tp->world;
+    d.done = d.epoch + 1;
+    d.ready = d.epoch + 2;
     d.rank = tp->rank; d.world = tp->world; d.max_elems = tp->max_elems;
     AB2_CUDA(cudaMalloc((void **)&tp->desc_dev, sizeof(d)));
     AB2_CUDA(cudaMemcpy(tp->desc_dev, &d, sizeof(d), cudaMemcpyHostToDevice));

@@ -13,6 +13,8 @@ struct ab2_tp_peer_desc {
     float *inbox[AB2_TP_MAX_WORLD];       // inbox[p]: rank p's inbox [2][world][max_elems] f32
     uint32_t *flags[AB2_TP_MAX_WORLD];    // flags[p]: rank p's arrival words [world]; I write flags[p][rank]
     uint32_t *epoch;                      // this rank's count of finished exchanges
+    uint32_t *done;                       // CTAs of the consuming kernel that have read the exchange
+    uint32_t *ready;                      // last exchange whose partial sums have all arrived (set by CTA 0)
     int rank, world;
     unsigned long long max_elems;
 };
