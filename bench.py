@@ -343,9 +343,10 @@ def main():
     ctx_mid = PROMPT + max(args.warmup, 3) + args.steps // 2
     # per GPU: a rank reads its 1/world share of the layer weights, head and KV
     step_bytes = (step_weight_bytes(cfg) + B * ctx_mid * kv_bytes_per_token(cfg)) // world
-    # embedding, per layer {norm+qkv, attention, o, norm+gate|up+SwiGLU, down} (tensor parallel: plus the two
-    # f32 residual adds after the all-reduces), norm+head, argmax, commit; NCCL's kernels are not counted
-    launches_per_step = (1 + cfg["n_layers"] * (5 if world == 1 else 7) + 3) if B == 1 else None
+    # embedding, per layer {norm+qkv, attention, o, norm+gate|up+SwiGLU, down} (tensor parallel: the same five,
+    # the partial sums travel in the projections' epilogues and the next GEMV's prologue), norm+head, argmax,
+    # commit; NCCL's all-gather of the logits shards is not counted
+    launches_per_step = (1 + cfg["n_layers"] * 5 + 3) if B == 1 else None
 
     line = {
         "metric": "INT4 decode tok/s", "value": round(B * 1e3 / ms_per_step, 2), "unit": "tokens/s",
