@@ -10,3 +10,4 @@ from . import dispatch  # noqa: F401
 from .model import AarambhModel, InferenceEngine, ModelConfig  # noqa: F401
 from . import parallel  # noqa: F401
 from .parallel import TensorParallel  # noqa: F401
+from . import gguf  # noqa: F401
