@@ -11,3 +11,4 @@ from .model import AarambhModel, InferenceEngine, ModelConfig  # noqa: F401
 from . import parallel  # noqa: F401
 from .parallel import TensorParallel  # noqa: F401
 from . import gguf  # noqa: F401
+from . import sessions  # noqa: F401
