@@ -111,7 +111,32 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(ClusterArgs a)
             if (t < n)
                 vraw[t] = *reinterpret_cast<const uint32_t *>((const char *)a.kv.v + (head_base + base + t) * HD + lane * 4);
     };
-    if (t0 < t1) stage_chunk(t0, min(32, t1 - t0));
+    // Short runs (at most 16 tokens per warp, the usual case at a few hundred cached
+    // tokens): LPT = 4 or 2 lanes share a token, each holding 32 or 64 of its 128 K
+    // bytes, so the score costs 1/LPT of the lane-per-token form and no lane idles.
+    const int lpt = tpw <= 8 ? 4 : (tpw <= 16 ? 2 : 1);
+    uint4 kq[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) kq[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (t0 < t1) {
+        if (lpt > 1) {
+            const int n = t1 - t0;
+            const int qj = lpt == 4 ? lane >> 2 : lane >> 1, qp = lpt == 4 ? lane & 3 : lane & 1;
+            const size_t trow = head_base + t0 + min(qj, n - 1);
+            const uint4 *kp = reinterpret_cast<const uint4 *>((const char *)a.kv.k + trow * HD + qp * (HD / lpt));
+            kq[0] = kp[0];
+            kq[1] = kp[1];
+            if (lpt == 2) { kq[2] = kp[2]; kq[3] = kp[3]; }
+            kscale_c = a.kv.ks[trow];
+            vscale_c = a.kv.vs[trow];
+#pragma unroll
+            for (int t = 0; t < 16; ++t)
+                if (t < n)
+                    vraw[t] = *reinterpret_cast<const uint32_t *>((const char *)a.kv.v + (head_base + t0 + t) * HD + lane * 4);
+        } else {
+            stage_chunk(t0, min(32, t1 - t0));
+        }
+    }
     // rotation table entries of this thread's pair (the position is known already)
     const int qh = tid >> 6, qd = tid & 63;
     const float qc = cs[qd], qsn = sn[qd];
@@ -212,8 +237,70 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(ClusterArgs a)
             wacc[warp][hh][half + 2 * lane + 1] = vd[3];
         }
     } else {
+        if (lpt > 1 && t0 < t1) {
+            const int n = t1 - t0;
+            const int qj = lpt == 4 ? lane >> 2 : lane >> 1, qp = lpt == 4 ? lane & 3 : lane & 1;
+            const int dims = HD / lpt;  // dims of this lane's part of the token
+            const bool valid = qj < n;
+            float sc[REP];
+#pragma unroll
+            for (int hh = 0; hh < REP; ++hh) sc[hh] = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                if (w * 16 < dims) {
+                    const uint32_t w4[4] = {kq[w].x, kq[w].y, kq[w].z, kq[w].w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float kf[4];
+                        i8x4_f32(w4[i], kf);
+#pragma unroll
+                        for (int hh = 0; hh < REP; ++hh) {
+                            const float4 qv = *reinterpret_cast<const float4 *>(&qs[hh][qp * dims + w * 16 + i * 4]);
+                            sc[hh] = fmaf(qv.x, kf[0], sc[hh]);
+                            sc[hh] = fmaf(qv.y, kf[1], sc[hh]);
+                            sc[hh] = fmaf(qv.z, kf[2], sc[hh]);
+                            sc[hh] = fmaf(qv.w, kf[3], sc[hh]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int hh = 0; hh < REP; ++hh) {
+                // the parts of a token's dot product, then the softmax over the tokens
+                float dot = sc[hh];
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                if (lpt == 4) dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                const float s = valid ? dot * kscale_c * a.scale : -INFINITY;
+                float cmx = s;
+#pragma unroll
+                for (int o = 2; o < 32; o <<= 1)
+                    if (o >= lpt) cmx = fmaxf(cmx, __shfl_xor_sync(0xffffffffu, cmx, o));
+                const float p = valid ? expf(s - cmx) : 0.f;
+                float psum = p;
+#pragma unroll
+                for (int o = 2; o < 32; o <<= 1)
+                    if (o >= lpt) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+                m_run[hh] = cmx;
+                l_run[hh] = psum;
+                if (qp == 0) ps[warp][qj][hh] = p * vscale_c;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                if (t < n) {
+                    float vf[4];
+                    i8x4_f32(vraw[t], vf);
+#pragma unroll
+                    for (int hh = 0; hh < REP; ++hh) {
+                        const float p = ps[warp][t][hh];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) acc[hh][j] = fmaf(p, vf[j], acc[hh][j]);
+                    }
+                }
+            }
+        }
         // ---- cached tokens of this warp, 32 at a time
-        for (int base = t0; base < t1; base += 32) {
+        for (int base = t0; lpt == 1 && base < t1; base += 32) {
             const int n = min(32, t1 - base);
             const bool valid = lane < n;
             if (base != t0) stage_chunk(base, n);

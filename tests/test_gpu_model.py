@@ -139,11 +139,11 @@ def test_fused_epilogue_path_matches_unfused_operators():
     assert rel_err(got[0].cpu().numpy(), ref.cpu().numpy()) < 1e-2
 
 
-@pytest.mark.parametrize("prompt_len", [5, 150, 300, 600])
+@pytest.mark.parametrize("prompt_len", [5, 120, 150, 300, 600])
 def test_decode_step_head_dim_128_int8_kv_matches_oracle(prompt_len):
     """The one-token step on the Large-class block shapes scaled down (head_dim
     128, grouped queries, INT8 KV, W4A16 weights, bf16): graph-replayed decode
-    steps (cluster attention over 1, 2, 4 and 8 context splits, RMSNorm fused into
+    steps (cluster attention over 1, 2, 4 and 8 context splits, with 4, 2 and 1 lanes per cached token, RMSNorm fused into
     the one-token GEMV) against the dense f32 oracle run over the whole sequence,
     and against the plain-launch decode of the same tokens."""
     cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
