@@ -25,6 +25,7 @@
 using namespace ab2;
 
 namespace ab2 {
+int device_sm_count();
 namespace {
 
 constexpr int HD = 128;
@@ -452,7 +453,10 @@ int attention_decode_cluster_device(ab2_kv *kv, int layer, const void *qkv, long
     a.qkv = (const __nv_bfloat16 *)qkv; a.out = (__nv_bfloat16 *)out; a.stride = stride;
     a.cos_t = cos_t; a.sin_t = sin_t; a.rope_pos = rope_pos;
     a.row0 = row0; a.h = kv->h; a.scale = scale;
-    const int want = (max_len + 127) / 128;
+    // context splits: enough CTAs to fill the GPU about twice, no more than one per 128 tokens
+    const int by_ctx = (max_len + 127) / 128;
+    const int by_gpu = (2 * device_sm_count() + nrows * kv->kvh - 1) / (nrows * kv->kvh);
+    const int want = std::min(by_ctx, by_gpu);
     a.nsplit = want <= 1 ? 1 : (want <= 2 ? 2 : (want <= 4 ? 4 : 8));
     dim3 grid(a.nsplit, kv->kvh, nrows);
     const int rep = kv->h / kv->kvh;

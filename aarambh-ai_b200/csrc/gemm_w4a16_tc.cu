@@ -24,9 +24,11 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "tcgen05_util.cuh"
 #include "w4a16_layout.cuh"
 
 using namespace ab2;
+using namespace ab2::tc;
 
 namespace ab2 {
 int device_status_word(int **out);
@@ -40,8 +42,6 @@ constexpr int TC_WSLOT_BYTES = 8 * TC_BLOCK_WORDS * 4;  // 8 row tiles of 16 = 1
 constexpr int TC_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
 constexpr int TC_THREADS = 320;
 
-__device__ __forceinline__ uint32_t sptr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
 struct TcShared {
     uint64_t wfull[TC_WSLOTS], wempty[TC_WSLOTS];
     uint64_t xfull[TC_MAX_STAGES], afull[TC_MAX_STAGES], sempty[TC_MAX_STAGES];
@@ -49,74 +49,6 @@ struct TcShared {
     uint32_t tmem_base;
     int failed;
 };
-
-__device__ __forceinline__ void bar_init(uint64_t *b, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(sptr(b)), "r"(count));
-}
-__device__ __forceinline__ void bar_arrive(uint64_t *b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(sptr(b)) : "memory");
-}
-__device__ __forceinline__ void bar_expect_tx(uint64_t *b, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(sptr(b)), "r"(bytes) : "memory");
-}
-// Bounded wait; also gives up as soon as another warp of the CTA has failed.
-__device__ __forceinline__ bool bar_wait(uint64_t *b, uint32_t parity, volatile int *failed) {
-    const uint32_t addr = sptr(b);
-    for (int spin = 0; spin < (1 << 20); ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if ((spin & 1023) == 1023 && *failed) return false;
-    }
-    *failed = 1;
-    return false;
-}
-
-__device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
-                     "r"(sptr(dst)), "l"(src), "r"(bytes), "r"(sptr(bar)) : "memory");
-}
-// 2-D tile load: coordinates (k element, token row); completion counted on `bar`.
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::
-            "r"(sptr(dst)), "l"(map), "r"(sptr(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle: 8-row groups are
-// 1024 bytes apart, the start address advances by 32 bytes per K = 16 step.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major): 1
-    d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset: 8 rows x 128 bytes
-    d |= (uint64_t)1 << 46;             // descriptor version
-    d |= (uint64_t)2 << 61;             // SWIZZLE_128B
-    return d;
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::
-            "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(sptr(bar)) : "memory");
-}
-
-__device__ __forceinline__ uint32_t bf16x2_add_(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("add.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t bf16x2_mul_(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
 
 template <int NTOK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -292,30 +224,6 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)(2 * NTOK)));
     }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-int make_x_map(CUtensorMap *map, const void *x, int M, int K, int ntok) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        AB2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-        AB2_REQUIRE(fn != nullptr && qres == cudaDriverEntryPointSuccess, AB2_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is unavailable");
-        encode = (EncodeTiledFn)fn;
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)ntok};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    AB2_REQUIRE(r == CUDA_SUCCESS, AB2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return AB2_OK;
 }
 
 template <int NTOK>

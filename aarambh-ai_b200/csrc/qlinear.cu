@@ -198,6 +198,9 @@ static cudaError_t launch_w4a16_m1(const ab2_qweight *w, const __nv_bfloat16 *x,
 constexpr int W4M1_MAX_K = 16384;
 constexpr int W4M1_PLAIN_MAX_K = 8192;
 
+int qlinear_w4a16_tc_decode(const ab2_qweight *w, const void *x, int M, void *y, const void *resid, int epi,
+                            float *partials, int *counters, int max_ctas, cudaStream_t s);
+
 template <int EPI>
 static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void *y, const void *resid,
                                cudaStream_t s, const float *norm_w = nullptr, float eps = 0.f,
@@ -218,6 +221,22 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     const int grid = (int)std::min<long long>(sc.max_ctas, std::max<long long>(1, (total / 8 + W4W_WARPS - 1) / W4W_WARPS));
     const uint32_t *wt = (const uint32_t *)w->codes;
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
+    // 17..64 tokens: the tensor-memory decode GEMM, 32 tokens per pass (the codes are unpacked once
+    // per pass whatever the token count; the warp kernel re-reads its activations for every block
+    // and needs a pass per 16 tokens).  Measured on the largest shape: 343 us per pass against
+    // 155 us per 16-token pass of the warp kernel, so it pays from 17 tokens.
+    constexpr int tc_min_m = 17;
+    if (M >= tc_min_m && EPI != W4_EPI_F32_PEER && !norm_w && w->N % 16 == 0) {
+        for (int m0 = 0; m0 < M; m0 += 32) {
+            const int mv = std::min(32, M - m0);
+            const char *xp = (const char *)x + (size_t)m0 * w->K * 2;
+            char *yp = (char *)y + (size_t)m0 * out_n * (EPI == W4_EPI_F32 ? 4 : 2);
+            const char *rp = resid ? (const char *)resid + (size_t)m0 * out_n * 2 : nullptr;
+            rc = qlinear_w4a16_tc_decode(w, xp, mv, yp, rp, EPI, sc.partials, sc.counters, sc.max_ctas, s);
+            if (rc != AB2_OK) return rc;
+        }
+        return AB2_OK;
+    }
     for (int m0 = 0; m0 < M; m0 += 16) {
         const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;
         __nv_bfloat16 *yp = EPI == W4_EPI_F32_PEER ? (__nv_bfloat16 *)y  // descriptor of the peer exchange (one pass)

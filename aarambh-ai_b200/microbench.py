@@ -90,7 +90,7 @@ def bench_gemv(pkg, args):
                 return
             t = time_graph(lambda: [lin(x) for lin in lins], 5, stream) / copies
             byt = w4_bytes(N, K) + 2 * M * (K + N)
-            print(json.dumps({"kernel": "gemv_w4a16_m1_kernel" if M == 1 else "gemv_w4a16_warp_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
+            print(json.dumps({"kernel": "gemv_w4a16_m1_kernel" if M == 1 else ("gemv_w4a16_warp_kernel" if M <= 16 else "gemv_w4a16_tc_kernel"), "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
                               "GBs": round(byt / t / 1e9, 1), "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}),
                   flush=True)
         del lins

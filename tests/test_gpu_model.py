@@ -171,3 +171,33 @@ def test_decode_step_head_dim_128_int8_kv_matches_oracle(prompt_len):
         plain = gpu.forward_decode_batch(np.array([[int(ids[pos])]]), [pos], cache2).float().cpu().numpy()[0, 0]
         assert rel_err(got, plain) < 1e-2, (prompt_len, s)
     assert pkg().device_status() == 0
+
+
+def test_batched_decode_rows_match_single_row_decode_on_the_w4a16_path():
+    """20 sequences decoded together (tensor-memory decode GEMM, one attention launch
+    for all rows) and 12 together (warp kernel with the residual and SwiGLU
+    epilogues) against each sequence decoded alone."""
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
+               max_seq=128)
+    gpu, _, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=64, capacity=64)
+    for B in (12, 20):
+        _batched_vs_single(gpu, cfg, B)
+
+
+def _batched_vs_single(gpu, cfg, B):
+    P, steps = 6, 3
+    rng = np.random.default_rng(21)
+    prompts = rng.integers(0, cfg["vocab"], (B, P))
+    nxt = rng.integers(0, cfg["vocab"], (steps, B))
+    together = gpu.empty_kv_cache_with_capacity(32, batch=B, dtype="int8")
+    for b in range(B):
+        gpu.forward_with_cache(prompts[b:b + 1], 0, together, row=b)
+    alone = [gpu.empty_kv_cache_with_capacity(32, dtype="int8") for _ in range(B)]
+    for b in range(B):
+        gpu.forward_with_cache(prompts[b:b + 1], 0, alone[b])
+    for s in range(steps):
+        lg = gpu.forward_decode_batch(nxt[s][:, None], [P + s] * B, together).float().cpu().numpy()
+        for b in range(B):
+            one = gpu.forward_decode_batch(nxt[s][b:b + 1, None], [P + s], alone[b]).float().cpu().numpy()
+            assert rel_err(lg[b], one[0]) < 2e-2, (s, b)
+    assert pkg().device_status() == 0

@@ -100,3 +100,23 @@ def test_w4a16_many_tokens_tensor_core_gemm(M, K, N):
     got = run(lin, x, torch.bfloat16)
     assert pkg().device_status() == 0
     assert rel_err(got, orc.linear(x, dense)) < TOL_BF16
+
+
+@pytest.mark.parametrize("M", [9, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 400), (14336, 512)])
+def test_w4a16_decode_gemm_on_tensor_memory(M, K, N):
+    """17..64 tokens take the tensor-memory decode GEMM (codes unpacked to 128 + q,
+    scale and zero point applied per group by the epilogue, channel tiles split
+    over K and finished by the last contributor), 9..16 the warp kernel's
+    two-token-tile form: against dequantise-then-matmul within 1e-2 relative; two
+    calls in a row give identical bits."""
+    rng = np.random.default_rng(8)
+    qw, scales, qz = make_w4a16(rng, N, K)
+    lin = pkg().QuantLinear.from_w4a16_gptq(qw, scales, qz, N, K, 128)
+    dense = orc.dequant_w4a16(qw, scales, qz, N, K, 128)
+    x = orc.round_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    got = run(lin, x, torch.bfloat16)
+    again = run(lin, x, torch.bfloat16)
+    assert pkg().device_status() == 0
+    assert rel_err(got, orc.linear(x, dense)) < TOL_BF16
+    assert np.array_equal(got, again)
