@@ -160,10 +160,12 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
                 asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(d.flags[p] + d.rank), "r"(exchange) : "memory");
                 const uint32_t *mine = d.flags[d.rank] + p;
                 bool ok = false;
-                for (int spin = 0; spin < (1 << 24); ++spin) {
+                const unsigned long long t0 = mbar_wall_ns();
+                for (int spin = 0;; ++spin) {
                     uint32_t v;
                     asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(mine) : "memory");
                     if ((int32_t)(v - exchange) >= 0) { ok = true; break; }
+                    if ((spin & 63) == 63 && mbar_wall_ns() - t0 > 2000000000ull) break;  // two seconds
                     __nanosleep(20);
                 }
                 if (!ok) peer_failed = 1;
@@ -174,10 +176,12 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
         } else {
             if (threadIdx.x == 0) {
                 bool ok = false;
-                for (int spin = 0; spin < (1 << 24); ++spin) {
+                const unsigned long long t0 = mbar_wall_ns();
+                for (int spin = 0;; ++spin) {
                     uint32_t v;
                     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(d.ready) : "memory");
                     if ((int32_t)(v - exchange) >= 0) { ok = true; break; }
+                    if ((spin & 63) == 63 && mbar_wall_ns() - t0 > 3000000000ull) break;  // CTA 0's own limit plus a margin
                     __nanosleep(20);
                 }
                 if (!ok) peer_failed = 1;

@@ -73,14 +73,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Bounded wait: false when the phase did not complete within the limit.  The
-// first probe is kept out of the loop so the common case costs one instruction.
+// Bounded wait: false when the phase did not complete within two seconds of wall
+// clock (%globaltimer; a probe may itself sleep, so counting probes bounds nothing).
+// The first probe is kept out of the loop so the common case costs one instruction.
+__device__ __forceinline__ unsigned long long mbar_wall_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
     if (mbar_try_wait(addr, parity)) return true;
-    for (int spin = 0; spin < (1 << 22); ++spin)
+    const unsigned long long t0 = mbar_wall_ns();
+    for (int spin = 0;; ++spin) {
         if (mbar_try_wait(addr, parity)) return true;
-    return false;
+        if ((spin & 15) == 15 && mbar_wall_ns() - t0 > 2000000000ull) return false;
+    }
 }
 // global -> shared bulk copy (16-byte aligned, size a multiple of 16), completion
 // counted in bytes on `bar`.

@@ -54,7 +54,8 @@ constexpr int DG_WSLOTS = 12;        // depth of a packed-weight ring (two block
 constexpr int DG_WSLOT_BYTES = 2 * W4_BLOCK_WORDS * 4;  // per ring; four rings (one per 32 channels) = ~100 KB in flight per SM
 constexpr int DG_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
 constexpr int DG_ONES_BYTES = 128 * 128;
-constexpr int DG_THREADS = 448;        // 14 warps
+constexpr int DG_MMA_WARPS = 2;        // MMA-issue warps, taking alternate units (warp 1 and the warps after the epilogue)
+constexpr int DG_THREADS = 448 + 32 * (DG_MMA_WARPS - 1);
 constexpr int DG_ACC = 4;             // accumulator pairs (D, S) in tensor memory
 constexpr int DG_PARAM_BUFS = 8;       // a buffer is rewritten 8 units later: its reader is long done
 
@@ -164,10 +165,12 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------- MMA issue
+    } else if (warp == 1 || warp >= 14) {
+        // ---------------------------------------------------------- MMA issue (alternate units per warp)
+        const uint32_t my_id = warp == 1 ? 0u : (uint32_t)(warp - 13);
         uint32_t use = 0;
         for (int u = rg.u0; u < rg.u1 && !*failed; ++u, ++use) {
+            if (use % DG_MMA_WARPS != my_id) continue;
             const int ab = use % DG_ACC;
             if (!bar_wait(&sh->accempty[ab], ((use / DG_ACC) & 1) ^ 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");

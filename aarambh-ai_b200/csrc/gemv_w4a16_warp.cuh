@@ -85,28 +85,16 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
         }
 }
 
-// Bounded wait on an mbarrier phase, one asm block (no divergence bookkeeping
-// around the common first-probe success).  Returns 0 when the limit ran out.
+// Bounded wait on an mbarrier phase (two seconds of wall clock).  Returns 0 when the
+// limit ran out.  The first probe is kept out of the loop so the common case costs
+// one instruction.
 __device__ __forceinline__ uint32_t mbar_wait_addr(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        " .reg .pred p;\n"
-        " .reg .u32 n;\n"
-        " mov.u32 n, 0x100000;\n"
-        "W4W_WAIT:\n"
-        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        " @p bra W4W_DONE;\n"
-        " sub.u32 n, n, 1;\n"
-        " setp.ne.u32 p, n, 0;\n"
-        " @p bra W4W_WAIT;\n"
-        "W4W_DONE:\n"
-        " selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
+    if (mbar_try_wait(bar, parity)) return 1u;
+    const unsigned long long t0 = mbar_wall_ns();
+    for (int spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return 1u;
+        if ((spin & 15) == 15 && mbar_wall_ns() - t0 > 2000000000ull) return 0u;
+    }
 }
 
 // When `go` is non-zero: arm `bar` for `bytes` and start the bulk copy of one

@@ -23,16 +23,28 @@ __device__ __forceinline__ void bar_arrive(uint64_t *b) {
 __device__ __forceinline__ void bar_expect_tx(uint64_t *b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(sptr(b)), "r"(bytes) : "memory");
 }
-// Bounded wait; also gives up as soon as another warp of the CTA has failed.
+// Bounded wait (two seconds of wall clock, read from %globaltimer; a probe may itself
+// sleep for a while, so counting probes bounds nothing); also gives up as soon as another
+// warp of the CTA has failed.
+__device__ __forceinline__ unsigned long long wall_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool bar_wait(uint64_t *b, uint32_t parity, volatile int *failed) {
     const uint32_t addr = sptr(b);
-    for (int spin = 0; spin < (1 << 20); ++spin) {
+    unsigned long long t0 = 0;
+    for (int spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if ((spin & 1023) == 1023 && *failed) return false;
+        if (spin == 0) t0 = wall_ns();
+        if ((spin & 15) == 15) {
+            if (*failed) return false;
+            if (wall_ns() - t0 > 2000000000ull) break;
+        }
     }
     *failed = 1;
     return false;

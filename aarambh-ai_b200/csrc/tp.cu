@@ -106,9 +106,15 @@ tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc
         st_release_sys(d.flags[p] + d.rank, e);  // "my partial sums of exchange e are in your inbox"
         const uint32_t *mine = d.flags[d.rank] + p;
         bool ok = false;
-        for (int spin = 0; spin < (1 << 24); ++spin) {
+        unsigned long long t0, now;
+        asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+        for (int spin = 0;; ++spin) {
             // the count only grows; a peer that is ahead has already passed e
             if ((int32_t)(ld_acquire_sys(mine) - e) >= 0) { ok = true; break; }
+            if ((spin & 63) == 63) {
+                asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+                if (now - t0 > 2000000000ull) break;  // two seconds
+            }
             __nanosleep(20);
         }
         if (!ok) failed = 1;
