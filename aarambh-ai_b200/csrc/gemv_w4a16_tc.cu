@@ -57,7 +57,12 @@ constexpr int DG_ONES_BYTES = 128 * 128;
 constexpr int DG_MMA_WARPS = 2;        // MMA-issue warps, taking alternate units (warp 1 and the warps after the epilogue)
 constexpr int DG_THREADS = 448 + 32 * (DG_MMA_WARPS - 1);
 constexpr int DG_ACC = 4;             // accumulator pairs (D, S) in tensor memory
-constexpr int DG_PARAM_BUFS = 8;       // a buffer is rewritten 8 units later: its reader is long done
+// An MMA-issue warp must see every phase of the barriers it waits on (a parity wait cannot tell
+// phase k from phase k + 2), so the stages, activation stages and accumulators a unit uses must come
+// back to the same warp: their counts are multiples of what DG_MMA_WARPS units use.
+static_assert(DG_STAGES % (2 * DG_MMA_WARPS) == 0 && DG_XSTAGES % (2 * DG_MMA_WARPS) == 0 && DG_ACC % DG_MMA_WARPS == 0,
+              "ring depths must be multiples of the MMA-issue warps' stride");
+constexpr int DG_PARAM_BUFS = 16;      // a buffer is rewritten 16 units later: its reader is long done
 
 struct DgShared {
     uint64_t wfull[4][DG_WSLOTS], wempty[4][DG_WSLOTS];
