@@ -453,11 +453,14 @@ int attention_decode_cluster_device(ab2_kv *kv, int layer, const void *qkv, long
     a.qkv = (const __nv_bfloat16 *)qkv; a.out = (__nv_bfloat16 *)out; a.stride = stride;
     a.cos_t = cos_t; a.sin_t = sin_t; a.rope_pos = rope_pos;
     a.row0 = row0; a.h = kv->h; a.scale = scale;
-    // context splits: enough CTAs to fill the GPU about twice, no more than one per 128 tokens
+    // context splits: one per 128 tokens (rounded up to a power of two, at most 8), but no more
+    // than keeps every CTA of the launch resident at once (two CTAs fit an SM): a second wave
+    // of clusters costs a whole kernel latency
     const int by_ctx = (max_len + 127) / 128;
-    const int by_gpu = (2 * device_sm_count() + nrows * kv->kvh - 1) / (nrows * kv->kvh);
-    const int want = std::min(by_ctx, by_gpu);
-    a.nsplit = want <= 1 ? 1 : (want <= 2 ? 2 : (want <= 4 ? 4 : 8));
+    const int want = by_ctx <= 1 ? 1 : (by_ctx <= 2 ? 2 : (by_ctx <= 4 ? 4 : 8));
+    const int fit = std::max(1, 2 * device_sm_count() / (nrows * kv->kvh));
+    const int cap = fit >= 8 ? 8 : (fit >= 4 ? 4 : (fit >= 2 ? 2 : 1));
+    a.nsplit = std::min(want, cap);
     dim3 grid(a.nsplit, kv->kvh, nrows);
     const int rep = kv->h / kv->kvh;
     cudaError_t e;
