@@ -272,14 +272,14 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
     if (max_len <= 0)
         for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + pending);
     int nsplit = 1;
-    if (S == 1 && pending == 0 && kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8 &&
-        st.q_h == kv->hd && st.q_b == (long long)kv->h * kv->hd && st.o_h == st.q_h && st.o_b == st.q_b) {
+    if (S == 1 && kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8 &&
+        st.q_h == kv->hd && st.o_h == st.q_h && st.o_b == (long long)kv->h * kv->hd) {
         // INT8 cache, head_dim 128: tensor-core flash-decode (attention_mma.cu)
         const int want = (148 * 6 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
         nsplit = std::max(1, std::min(std::min(want, (max_len + 63) / 64), kv->max_splits));
         a.nsplit = nsplit;
         int rc = attention_decode_mma_device(kv, layer, q, out, row0, nrows, scale, dtype, nsplit, kv->part_acc,
-                                             kv->part_ml, s);
+                                             kv->part_ml, pending, st.q_b, s);
         if (rc != AB2_OK) return rc;
         if (nsplit > 1) attn_merge_kernel<<<dim3(kv->h, nrows), kv->hd, 0, s>>>(a, kv->hd);
         AB2_LAUNCH_CHECK();
@@ -438,7 +438,7 @@ AB2_API int ab2_attention_decode_static(const ab2_kv *kv, int layer, const void 
     dim3 grid(a.nsplit, kv->kvh, nrows);
     if (mma_path) {
         rc = attention_decode_mma_device(kv, layer, q_dev, out_dev, row0, nrows, scale, dtype, a.nsplit, a.part_acc,
-                                         a.part_ml, s);
+                                         a.part_ml, 0, (long long)kv->h * kv->hd, s);
         if (rc != AB2_OK) return rc;
         if (a.nsplit > 1) attn_merge_kernel<<<dim3(kv->h, nrows), kv->hd, 0, s>>>(a, kv->hd);
         AB2_LAUNCH_CHECK();

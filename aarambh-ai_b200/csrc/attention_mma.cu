@@ -27,8 +27,10 @@ namespace {
 
 struct MmaAttnArgs {
     KvView kv;
-    const void *q;  // [rows][h][128]
+    const void *q;  // head (row, head) at row * q_stride + head * 128
+    long long q_stride;
     int row0, h, rep, nsplit, dtype;
+    int pending;    // appended, not yet committed tokens per row: they are attended too
     float scale;
     float *part_acc, *part_ml;
     void *out;      // used when nsplit == 1
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(MmaAttnArgs a) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int split = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = a.row0 + rrow;
-    const int len = a.kv.lens[row];
+    const int len = a.kv.lens[row] + a.pending;
     int per = (len + a.nsplit - 1) / a.nsplit;
     per = (per + 63) & ~63;  // whole 16-token blocks for each of the four warps
     const int t0 = split * per, t1 = min(len, t0 + per);
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(MmaAttnArgs a) {
     // covers d = c*32 + 4s + {0,1} (a0) and {2,3} (a2).  Rows >= rep are zero.
     uint32_t qa0[8], qa2[8];
     {
-        const size_t qb = ((size_t)rrow * a.h + (size_t)kvhead * a.rep + g) * HD + c * 32;
+        const size_t qb = (size_t)rrow * a.q_stride + ((size_t)kvhead * a.rep + g) * HD + c * 32;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
@@ -266,12 +268,13 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(MmaAttnArgs a) {
 // kernel serves (the caller then uses the general kernel).
 int attention_decode_mma_device(const ab2_kv *kv, int layer, const void *q, void *out, int row0, int nrows,
                                 float scale, ab2_dtype dtype, int nsplit, float *part_acc, float *part_ml,
-                                cudaStream_t s) {
+                                int pending, long long q_stride, cudaStream_t s) {
     if (kv->dtype != AB2_KV_INT8 || kv->hd != 128 || kv->h / kv->kvh > 8) return AB2_ERR_UNSUPPORTED;
     MmaAttnArgs a;
     a.kv = kv_view(kv, layer);
     a.q = q; a.out = out; a.row0 = row0; a.h = kv->h; a.rep = kv->h / kv->kvh; a.nsplit = nsplit;
     a.dtype = (int)dtype; a.scale = scale; a.part_acc = part_acc; a.part_ml = part_ml;
+    a.pending = pending; a.q_stride = q_stride;
     attn_decode_mma_kernel<<<dim3(nsplit, kv->kvh, nrows), 128, 0, s>>>(a);
     AB2_LAUNCH_CHECK();
     return AB2_OK;

@@ -50,11 +50,13 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
                             int row0, int nrows, float scale, ab2_dtype dtype, AttnStrides st,
                             int len_hint, cudaStream_t s);
 
-// Tensor-core INT8 flash-decode (head_dim 128): q, out [nrows][h][128]; partials
-// go to the given split scratch, merged by the caller when nsplit > 1.
+// Tensor-core INT8 flash-decode (head_dim 128): query head (row, head) sits at
+// row * q_stride + head * 128, out is [nrows][h][128]; `pending` appended but
+// uncommitted tokens per row are attended too; partials go to the given split
+// scratch, merged by the caller when nsplit > 1.
 int attention_decode_mma_device(const ab2_kv *kv, int layer, const void *q, void *out, int row0, int nrows,
                                 float scale, ab2_dtype dtype, int nsplit, float *part_acc, float *part_ml,
-                                cudaStream_t s);
+                                int pending, long long q_stride, cudaStream_t s);
 int attention_decode_fused_device(ab2_kv *kv, int layer, const void *qkv, long long stride, void *out,
                                   int row0, int nrows, float scale, ab2_dtype dtype, const float *cos_t,
                                   const float *sin_t, const int *rope_pos, int len_hint, cudaStream_t s);

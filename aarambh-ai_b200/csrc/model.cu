@@ -61,7 +61,7 @@ struct ab2_model {
     void *x, *xn, *qkv, *attn, *proj, *gu, *hid;
     int *positions;        // [max rows] explicit RoPE offsets
     int *positions_host;   // pinned
-    std::map<std::tuple<const void *, const void *, int, int, const void *, const void *>, StepGraph> graphs;
+    std::map<std::tuple<const void *, const void *, int, int, const void *, const void *, int>, StepGraph> graphs;
 };
 
 namespace ab2 {
@@ -138,6 +138,16 @@ static int launch_rope_q(ab2_model *m, int T, int S, int row0, const int *base, 
     return AB2_OK;
 }
 
+// Decode attention as rotation + append + tensor-core flash-decode (+ merge) instead of the
+// one-launch CUDA-core kernels.  The one-launch kernels win while the launch count is what
+// matters; they are bound by the int8 -> float conversion once a step reads many cached tokens.
+static bool decode_attention_on_tensor_cores(const ab2_kv *kv, int nrows, int max_len) {
+    if (kv->dtype != AB2_KV_INT8 || kv->hd != 128 || kv->h / kv->kvh > 8) return false;
+    static const char *force = getenv("AB2_DECODE_ATTN");
+    if (force) return strcmp(force, "mma") == 0;
+    return nrows >= 2 ? nrows * (long long)max_len > 1024 : max_len > 6144;
+}
+
 #define STEP(expr)                     \
     do {                               \
         int _rc = (expr);              \
@@ -186,11 +196,11 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         LayerWeights &L = m->layers[l];
         if (pending) STEP(consume(L.wqkv, L.norm1, m->qkv, 0));
         else STEP(norm_linear(m, L.wqkv, xcur, L.norm1, T, m->qkv, 0, s));
-        if (S == 1) {
+        int max_len = len_hint;
+        if (S == 1 && max_len <= 0)
+            for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + 1);
+        if (S == 1 && !decode_attention_on_tensor_cores(kv, nrows, max_len)) {
             // decode: RoPE, KV append, attention and split merge in one launch
-            int max_len = len_hint;
-            if (max_len <= 0)
-                for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + 1);
             if (attention_decode_cluster_eligible(kv, m->dtype, max_len))
                 STEP(attention_decode_cluster_device(kv, l, m->qkv, qkv_stride, m->attn, row0, nrows, scale, m->cos_t,
                                                      m->sin_t, rope_base == kv->lens_dev ? nullptr : rope_base,
@@ -543,7 +553,15 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
         if (rc != AB2_OK) return rc;
         return kv_commit_device(kv, 1, row0, nrows, s);
     }
-    auto key = std::make_tuple((const void *)kv, (const void *)ids_dev, row0, nrows, (const void *)logits_dev, (const void *)argmax_dev);
+    // The attention launch is shaped by the context length (splits, kernel choice), which a captured
+    // launch cannot read: graphs are kept per power-of-two bound of the longest row.
+    int longest = 1;
+    for (int r = row0; r < row0 + nrows; ++r) longest = std::max(longest, kv->lens_host[r] + 1);
+    int len_bound = 512;
+    while (len_bound < longest) len_bound <<= 1;
+    len_bound = std::min(len_bound, kv->cap);
+    auto key = std::make_tuple((const void *)kv, (const void *)ids_dev, row0, nrows, (const void *)logits_dev,
+                               (const void *)argmax_dev, len_bound);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         cudaGraph_t graph = nullptr;
@@ -551,7 +569,7 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
         if (rc != AB2_OK) return rc;
         AB2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         g_pdl_launch = m->fused_epilogues;  // every kernel of the fast path takes part in the chain
-        rc = forward_launches(m, kv, ids_dev, 1, row0, nrows, kv->lens_dev, logits_dev ? 1 : 0, logits_dev, argmax_dev, kv->cap, s);
+        rc = forward_launches(m, kv, ids_dev, 1, row0, nrows, kv->lens_dev, logits_dev ? 1 : 0, logits_dev, argmax_dev, len_bound, s);
         if (rc == AB2_OK) {
             // lengths advance inside the graph; the host mirror is advanced per replay
             std::vector<int> keep(kv->lens_host, kv->lens_host + kv->B);

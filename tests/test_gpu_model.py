@@ -139,13 +139,14 @@ def test_fused_epilogue_path_matches_unfused_operators():
     assert rel_err(got[0].cpu().numpy(), ref.cpu().numpy()) < 1e-2
 
 
-@pytest.mark.parametrize("prompt_len", [5, 120, 150, 300, 600])
+@pytest.mark.parametrize("prompt_len", [5, 120, 150, 300, 510, 600])
 def test_decode_step_head_dim_128_int8_kv_matches_oracle(prompt_len):
     """The one-token step on the Large-class block shapes scaled down (head_dim
     128, grouped queries, INT8 KV, W4A16 weights, bf16): graph-replayed decode
     steps (cluster attention over 1, 2, 4 and 8 context splits, with 4, 2 and 1 lanes per cached token, RMSNorm fused into
     the one-token GEMV) against the dense f32 oracle run over the whole sequence,
-    and against the plain-launch decode of the same tokens."""
+    and against the plain-launch decode of the same tokens.  From 510 cached tokens the
+    steps cross a power of two of the context length, where the step graph is captured anew."""
     cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
                max_seq=1024)
     gpu, cpu, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=640, capacity=640)
@@ -200,4 +201,35 @@ def _batched_vs_single(gpu, cfg, B):
         for b in range(B):
             one = gpu.forward_decode_batch(nxt[s][b:b + 1, None], [P + s], alone[b]).float().cpu().numpy()
             assert rel_err(lg[b], one[0]) < 2e-2, (s, b)
+    assert pkg().device_status() == 0
+
+
+def test_batched_decode_step_over_ragged_long_rows_matches_oracle():
+    """Four rows of 300, 257, 64 and 290 cached tokens decoded together: enough cached
+    tokens per step that attention runs as rotation + append + the tensor-core
+    flash-decode over uncommitted tokens (context splits, one of them empty for the
+    short row) + merge.  Graph-replayed steps against the dense f32 oracle of each
+    sequence."""
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
+               max_seq=512)
+    lens, steps = [300, 257, 64, 290], 3
+    B = len(lens)
+    gpu, cpu, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=320, batch=B, capacity=320)
+    seqs = [prompt(cfg["vocab"], n + steps, 31 + i) for i, n in enumerate(lens)]
+    refs = [cpu.forward(s[None], [0], row0=i)[0] for i, s in enumerate(seqs)]   # [S, vocab] each
+    cache = gpu.empty_kv_cache_with_capacity(max(lens) + steps + 2, batch=B, dtype="int8")
+    for b in range(B):
+        gpu.forward_with_cache(seqs[b][None, :lens[b]], 0, cache, row=b)
+    side = torch.cuda.Stream()
+    logits = torch.empty((B, cfg["vocab"]), dtype=torch.bfloat16, device="cuda")
+    tok = torch.empty(B, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for s in range(steps):
+        with torch.cuda.stream(side):
+            tok.copy_(torch.tensor([int(seqs[b][lens[b] + s]) for b in range(B)], dtype=torch.int32))
+            gpu.decode_step(tok, cache, logits, None)
+            side.synchronize()
+        got = logits.float().cpu().numpy()
+        for b in range(B):
+            assert rel_err(got[b], refs[b][lens[b] + s]) < 2e-2, (s, b)
     assert pkg().device_status() == 0
