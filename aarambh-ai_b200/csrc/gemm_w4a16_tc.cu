@@ -35,7 +35,9 @@ int device_status_word(int **out);
 int device_sm_count();
 namespace {
 
-constexpr int TC_MAX_STAGES = 4;      // operand stages of 64 K-elements (3 for 256-token tiles)
+constexpr int TC_STAGES = 3;          // operand-A (unpacked weight) stages of 64 K-elements
+constexpr int TC_MAX_XSTAGES = 8;     // operand-B (activation) stages: a ring of its own, 128 KB deep, because an
+                                      // activation tile takes about three stage times to arrive from L2
 constexpr int TC_WSLOTS = 4;          // packed-weight ring slots (one quantisation group each)
 constexpr int TC_BLOCK_WORDS = 272;   // 16 rows x 16 code words + 16 parameter words
 constexpr int TC_WSLOT_BYTES = 8 * TC_BLOCK_WORDS * 4;  // 8 row tiles of 16 = 128 channels
@@ -44,24 +46,29 @@ constexpr int TC_THREADS = 320;
 
 struct TcShared {
     uint64_t wfull[TC_WSLOTS], wempty[TC_WSLOTS];
-    uint64_t xfull[TC_MAX_STAGES], afull[TC_MAX_STAGES], sempty[TC_MAX_STAGES];
+    uint64_t xfull[TC_MAX_XSTAGES], xempty[TC_MAX_XSTAGES], afull[TC_STAGES], sempty[TC_STAGES];
     uint64_t accfull[2], accempty[2];  // two accumulators: the epilogue of a tile overlaps the next tile's MMAs
     uint32_t tmem_base;
     int failed;
 };
 
 template <int NTOK>
+__host__ __device__ constexpr int tc_xstages() {
+    return (128 * 1024) / (NTOK * 128) < TC_MAX_XSTAGES ? (128 * 1024) / (NTOK * 128) : TC_MAX_XSTAGES;
+}
+
+template <int NTOK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CUtensorMap xmap,
                      __nv_bfloat16 *__restrict__ y, int N, int K, int M, int *status) {
     constexpr int B_BYTES = NTOK * 128;
-    constexpr int TC_STAGES = NTOK > 128 ? 3 : 4;
+    constexpr int XST = tc_xstages<NTOK>();
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((128u >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *a_st = smem;                                   // [TC_STAGES][TC_A_BYTES]
-    uint8_t *b_st = a_st + TC_STAGES * TC_A_BYTES;          // [TC_STAGES][B_BYTES]
-    uint8_t *w_ring = b_st + TC_STAGES * B_BYTES;           // [TC_WSLOTS][TC_WSLOT_BYTES]
+    uint8_t *b_st = a_st + TC_STAGES * TC_A_BYTES;          // [XST][B_BYTES]
+    uint8_t *w_ring = b_st + XST * B_BYTES;                 // [TC_WSLOTS][TC_WSLOT_BYTES]
     TcShared *sh = (TcShared *)(w_ring + TC_WSLOTS * TC_WSLOT_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -72,7 +79,8 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TC_WSLOTS; ++i) { bar_init(&sh->wfull[i], 1); bar_init(&sh->wempty[i], 128); }
-        for (int i = 0; i < TC_STAGES; ++i) { bar_init(&sh->xfull[i], 1); bar_init(&sh->afull[i], 128); bar_init(&sh->sempty[i], 1); }
+        for (int i = 0; i < TC_STAGES; ++i) { bar_init(&sh->afull[i], 128); bar_init(&sh->sempty[i], 1); }
+        for (int i = 0; i < XST; ++i) { bar_init(&sh->xfull[i], 1); bar_init(&sh->xempty[i], 1); }
         for (int i = 0; i < 2; ++i) { bar_init(&sh->accfull[i], 1); bar_init(&sh->accempty[i], 4); }
         sh->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -102,10 +110,10 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                         bulk_copy(w_ring + ws * TC_WSLOT_BYTES + b * TC_BLOCK_WORDS * 4,
                                   wt + ((size_t)(nt * 8 + b) * G + g) * TC_BLOCK_WORDS, TC_BLOCK_WORDS * 4, &sh->wfull[ws]);
                     for (int half = 0; half < 2; ++half, ++suse) {
-                        const int s = suse % TC_STAGES;
-                        if (!bar_wait(&sh->sempty[s], ((suse / TC_STAGES) & 1) ^ 1, failed)) break;
-                        bar_expect_tx(&sh->xfull[s], B_BYTES);
-                        tma_load_2d(b_st + s * B_BYTES, &xmap, g * 128 + half * 64, mt * NTOK, &sh->xfull[s]);
+                        const int xs = suse % XST;
+                        if (!bar_wait(&sh->xempty[xs], ((suse / XST) & 1) ^ 1, failed)) break;
+                        bar_expect_tx(&sh->xfull[xs], B_BYTES);
+                        tma_load_2d(b_st + xs * B_BYTES, &xmap, g * 128 + half * 64, mt * NTOK, &sh->xfull[xs]);
                     }
                 }
             }
@@ -119,17 +127,17 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t tacc = tmem + (uint32_t)(ab * NTOK);
             for (int ks = 0; ks < 2 * G && !*failed; ++ks, ++suse) {
-                const int s = suse % TC_STAGES;
-                const uint32_t par = (suse / TC_STAGES) & 1;
-                if (!bar_wait(&sh->xfull[s], par, failed)) break;
-                if (!bar_wait(&sh->afull[s], par, failed)) break;
+                const int s = suse % TC_STAGES, xs = suse % XST;
+                if (!bar_wait(&sh->xfull[xs], (suse / XST) & 1, failed)) break;
+                if (!bar_wait(&sh->afull[s], (suse / TC_STAGES) & 1, failed)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 if (lane == 0) {
-                    const uint32_t a0 = sptr(a_st + s * TC_A_BYTES), b0 = sptr(b_st + s * B_BYTES);
+                    const uint32_t a0 = sptr(a_st + s * TC_A_BYTES), b0 = sptr(b_st + xs * B_BYTES);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         umma_bf16(tacc, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (ks | k) != 0);
-                    umma_commit(&sh->sempty[s]);  // frees both operand stages when the MMAs retire
+                    umma_commit(&sh->sempty[s]);  // the operand stages are free when the MMAs retire
+                    umma_commit(&sh->xempty[xs]);
                 }
                 __syncwarp();
             }
@@ -234,8 +242,7 @@ int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t 
     CUtensorMap map;
     rc = make_x_map(&map, x, M, w->K, NTOK);
     if (rc != AB2_OK) return rc;
-    constexpr int stages = NTOK > 128 ? 3 : 4;
-    const size_t smem = 1024 + stages * TC_A_BYTES + stages * NTOK * 128 + TC_WSLOTS * TC_WSLOT_BYTES + sizeof(TcShared);
+    const size_t smem = 1024 + TC_STAGES * TC_A_BYTES + tc_xstages<NTOK>() * NTOK * 128 + TC_WSLOTS * TC_WSLOT_BYTES + sizeof(TcShared);
     static bool configured = false;
     if (!configured) {
         AB2_CUDA(cudaFuncSetAttribute(gemm_w4a16_tc_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

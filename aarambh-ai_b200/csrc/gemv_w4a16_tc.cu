@@ -319,6 +319,13 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             }
             if (finish) {
                 const int n = nt * 128 + row;
+                // the residual may alias the output: its values are all read before the first store
+                float rv[EPI == W4_EPI_ADD ? NTOK : 1];
+                if (EPI == W4_EPI_ADD) {
+#pragma unroll
+                    for (int j = 0; j < NTOK; ++j)
+                        rv[j] = (j < M && n < N) ? __bfloat162float(resid[(size_t)j * N + n]) : 0.f;
+                }
 #pragma unroll
                 for (int j = 0; j < NTOK; ++j) {
                     if (EPI == W4_EPI_SWIGLU) {
@@ -334,7 +341,7 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                         if (EPI == W4_EPI_F32) {
                             reinterpret_cast<float *>(y)[o] = v;
                         } else {
-                            if (EPI == W4_EPI_ADD) v = __bfloat162float(resid[o]) + __bfloat162float(__float2bfloat16_rn(v));
+                            if (EPI == W4_EPI_ADD) v = rv[EPI == W4_EPI_ADD ? j : 0] + __bfloat162float(__float2bfloat16_rn(v));
                             y[o] = __float2bfloat16_rn(v);
                         }
                     }

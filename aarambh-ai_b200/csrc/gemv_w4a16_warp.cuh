@@ -49,6 +49,18 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
         peer_world = peers->world;
         peer_off = ((size_t)((*peers->epoch + 1) & 1u) * peer_world + peers->rank) * peers->max_elems;
     }
+    // The residual may alias the output (the stream is updated in place), so loads left between
+    // the stores could not be moved ahead of them: all residual values are read first.
+    float rv[NT][4];
+    if (EPI == W4_EPI_ADD) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int tok = 8 * t + 2 * c + (q & 1), row = tile * 16 + r + 8 * (q >> 1);
+                rv[t][q] = (tok < M && row < N) ? __bfloat162float(resid[(size_t)tok * N + row]) : 0.f;
+            }
+    }
 #pragma unroll
     for (int t = 0; t < NT; ++t)
 #pragma unroll
@@ -77,7 +89,7 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
                         for (int p = 0; p < peer_world; ++p) peers->inbox[p][peer_off + o] = v;
                     } else {
                         if (EPI == W4_EPI_ADD)  // residual + bf16(projection), as residual + x does
-                            v = __bfloat162float(resid[o]) + __bfloat162float(__float2bfloat16_rn(v));
+                            v = rv[t][2 * h + i] + __bfloat162float(__float2bfloat16_rn(v));
                         y[o] = __float2bfloat16_rn(v);
                     }
                 }
