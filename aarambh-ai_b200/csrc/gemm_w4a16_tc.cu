@@ -8,10 +8,17 @@
 // dimension (operand B = activations), so any token count is a legal N and the
 // weights are dequantised once per (channel tile, token tile).  One CTA per SM,
 // persistent over tiles, warp-specialised:
-//   warp 0      producer: bulk copies of packed weight blocks into a ring, TMA
-//               tile loads of X (128-byte swizzle) into the operand-B stages
+//   warp 0      producer of the packed weights: one ring slot per quantisation
+//               group, lane b issues the bulk copy of 16-channel block b
+//   warp 10     producer of the activations: TMA tile loads of X (128-byte
+//               swizzle) into the operand-B stages
 //   warp 1      allocates tensor memory, issues tcgen05.mma (K = 16 per
-//               instruction, 64 per stage), commits stage / accumulator barriers
+//               instruction, 64 per stage), commits stage / accumulator barriers.
+//               A tcgen05 instruction costs the issuing thread on the order of a
+//               hundred cycles, about what a 128 x 256 x 16 MMA takes to execute:
+//               tiles are 256 tokens wide where the token count allows, and the
+//               operand rings of that tile size have equal depth so that one
+//               commit per stage frees both operands
 //   warps 2-5   dequantise: thread = output channel; nibbles -> bf16 (128 + q by
 //               one logic op, minus (128 + z) exactly, times the bf16 scale, i.e.
 //               the round-to-nearest bf16 of (q - z) * s) written into the
@@ -35,14 +42,14 @@ int device_status_word(int **out);
 int device_sm_count();
 namespace {
 
-constexpr int TC_STAGES = 3;          // operand-A (unpacked weight) stages of 64 K-elements
+constexpr int TC_STAGES = 4;          // operand-A (unpacked weight) stages of 64 K-elements
 constexpr int TC_MAX_XSTAGES = 8;     // operand-B (activation) stages: a ring of its own, 128 KB deep, because an
                                       // activation tile takes about three stage times to arrive from L2
-constexpr int TC_WSLOTS = 4;          // packed-weight ring slots (one quantisation group each)
+constexpr int TC_WSLOTS = 3;          // packed-weight ring slots (one quantisation group each)
 constexpr int TC_BLOCK_WORDS = 272;   // 16 rows x 16 code words + 16 parameter words
 constexpr int TC_WSLOT_BYTES = 8 * TC_BLOCK_WORDS * 4;  // 8 row tiles of 16 = 128 channels
 constexpr int TC_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
-constexpr int TC_THREADS = 320;
+constexpr int TC_THREADS = 352;
 
 struct TcShared {
     uint64_t wfull[TC_WSLOTS], wempty[TC_WSLOTS];
@@ -54,7 +61,7 @@ struct TcShared {
 
 template <int NTOK>
 __host__ __device__ constexpr int tc_xstages() {
-    return (128 * 1024) / (NTOK * 128) < TC_MAX_XSTAGES ? (128 * 1024) / (NTOK * 128) : TC_MAX_XSTAGES;
+    return NTOK > 128 ? TC_STAGES : TC_MAX_XSTAGES;
 }
 
 template <int NTOK>
@@ -96,25 +103,39 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0) {
-        // ---------------------------------------------------------- producer
+        // ---------------------------------------------------------- producer of the packed weights
+        // One slot per quantisation group; lane b issues the bulk copy of block b, so the eight
+        // copies of a group leave in parallel instead of one after the other from a single thread.
+        uint32_t wuse = 0;
+        for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
+            const int nt = it / m_tiles;
+            const int nblk = min(8, tiles16 - nt * 8);
+            for (int g = 0; g < G && !*failed; ++g, ++wuse) {
+                const int ws = wuse % TC_WSLOTS;
+                int ok = 1;
+                if (lane == 0) {
+                    ok = bar_wait(&sh->wempty[ws], ((wuse / TC_WSLOTS) & 1) ^ 1, failed) ? 1 : 0;
+                    if (ok) bar_expect_tx(&sh->wfull[ws], (uint32_t)nblk * TC_BLOCK_WORDS * 4);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (lane < nblk)
+                    bulk_copy(w_ring + ws * TC_WSLOT_BYTES + lane * TC_BLOCK_WORDS * 4,
+                              wt + ((size_t)(nt * 8 + lane) * G + g) * TC_BLOCK_WORDS, TC_BLOCK_WORDS * 4, &sh->wfull[ws]);
+            }
+        }
+    } else if (warp == TC_THREADS / 32 - 1) {
+        // ---------------------------------------------------------- producer of the activation tiles
         if (lane == 0) {
-            uint32_t wuse = 0, suse = 0;
+            uint32_t suse = 0;
             for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
-                const int nt = it / m_tiles, mt = it % m_tiles;
-                const int nblk = min(8, tiles16 - nt * 8);
-                for (int g = 0; g < G && !*failed; ++g, ++wuse) {
-                    const int ws = wuse % TC_WSLOTS;
-                    if (!bar_wait(&sh->wempty[ws], ((wuse / TC_WSLOTS) & 1) ^ 1, failed)) break;
-                    bar_expect_tx(&sh->wfull[ws], (uint32_t)nblk * TC_BLOCK_WORDS * 4);
-                    for (int b = 0; b < nblk; ++b)
-                        bulk_copy(w_ring + ws * TC_WSLOT_BYTES + b * TC_BLOCK_WORDS * 4,
-                                  wt + ((size_t)(nt * 8 + b) * G + g) * TC_BLOCK_WORDS, TC_BLOCK_WORDS * 4, &sh->wfull[ws]);
-                    for (int half = 0; half < 2; ++half, ++suse) {
-                        const int xs = suse % XST;
-                        if (!bar_wait(&sh->xempty[xs], ((suse / XST) & 1) ^ 1, failed)) break;
-                        bar_expect_tx(&sh->xfull[xs], B_BYTES);
-                        tma_load_2d(b_st + xs * B_BYTES, &xmap, g * 128 + half * 64, mt * NTOK, &sh->xfull[xs]);
-                    }
+                const int mt = it % m_tiles;
+                for (int ks = 0; ks < 2 * G && !*failed; ++ks, ++suse) {
+                    const int xs = suse % XST;
+                    // rings of equal depth share one "stage free" barrier (one commit per stage instead of two)
+                    if (!bar_wait(XST == TC_STAGES ? &sh->sempty[xs] : &sh->xempty[xs], ((suse / XST) & 1) ^ 1, failed)) break;
+                    bar_expect_tx(&sh->xfull[xs], B_BYTES);
+                    tma_load_2d(b_st + xs * B_BYTES, &xmap, ks * 64, mt * NTOK, &sh->xfull[xs]);
                 }
             }
         }
@@ -137,7 +158,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                     for (int k = 0; k < 4; ++k)
                         umma_bf16(tacc, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (ks | k) != 0);
                     umma_commit(&sh->sempty[s]);  // the operand stages are free when the MMAs retire
-                    umma_commit(&sh->xempty[xs]);
+                    if (XST != TC_STAGES) umma_commit(&sh->xempty[xs]);
                 }
                 __syncwarp();
             }
@@ -187,7 +208,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                 }
             }
         }
-    } else {
+    } else if (warp < 10) {
         // ---------------------------------------------------------- epilogue
         const int quad = warp & 3;
         uint32_t tuse = 0;
