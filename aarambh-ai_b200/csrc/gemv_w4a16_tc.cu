@@ -5,16 +5,19 @@
 //   Y[M, N] = X[M, K] . W^T,  W packed 4-bit in tile-major blocks (w4a16_layout.cuh)
 //
 // The 128 output channels of a channel tile are the M dimension of the MMA, the
-// tokens (padded to NTOK) its N dimension.  Operand A is NOT the dequantised
-// weight: the unpack warps only turn codes into bf16 128 + q (0x4300 | q) and
-// write them to the swizzled operand stage.  Scale and zero point are applied
-// per quantisation group in f32 by the epilogue warps: after the MMAs of a group
-//   d[c][t] = sum_k x[t][k] (128 + q[c][k])        (tensor memory, buffer D)
-//   S[t]    = sum_k x[t][k]                        (a second MMA against an all-ones A tile, buffer S)
-// and the group adds  scale[c] * (d[c][t] - (128 + zero[c]) * S[t])  to the
-// running f32 output kept in the epilogue threads' registers (thread = channel).
-// Both accumulators are double-buffered in tensor memory, so the epilogue of a
-// group overlaps the MMAs of the next.
+// tokens (padded to NTOK) its N dimension.  Operand A is the integer q - zero in
+// bf16, not the dequantised weight: the unpack warps turn codes into 128 + q
+// (0x4300 | q, one shift and one logic op per pair of codes), add the channel's
+// -(128 + zero) as one packed bf16 add (exact: both are small integers) and write
+// the pair to the swizzled operand stage.  The scale is applied per quantisation
+// group in f32 by the epilogue warps: after the MMAs of a group
+//   d[c][t] = sum_k x[t][k] (q[c][k] - zero[c])        (tensor memory)
+// and the group adds scale[c] * d[c][t] to the running f32 output kept in the
+// epilogue threads' registers (thread = channel).  Four accumulators rotate in
+// tensor memory, so the epilogue of a group overlaps the MMAs of the next ones.
+// (An earlier form kept the zero point out of operand A and obtained the
+// per-group activation sums from a second MMA against an all-ones tile; halving
+// the MMA count this way gave 3-8 % per GEMM and 8 % on the 32-row decode step.)
 //
 // Work is the sequence of (channel tile, group) units in tile-major order, cut
 // into one contiguous range per CTA (one CTA per SM), so small weights are split
@@ -53,7 +56,6 @@ constexpr int DG_XSTAGES = 8;        // operand-B (activation) stages: small, so
 constexpr int DG_WSLOTS = 12;        // depth of a packed-weight ring (two blocks = 32 channels of one unit per slot)
 constexpr int DG_WSLOT_BYTES = 2 * W4_BLOCK_WORDS * 4;  // per ring; four rings (one per 32 channels) = ~100 KB in flight per SM
 constexpr int DG_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
-constexpr int DG_ONES_BYTES = 128 * 128;
 constexpr int DG_MMA_WARPS = 2;        // MMA-issue warps, taking alternate units (warp 1 and the warps after the epilogue)
 constexpr int DG_THREADS = 448 + 32 * (DG_MMA_WARPS - 1);
 constexpr int DG_ACC = 4;             // accumulator pairs (D, S) in tensor memory
@@ -119,12 +121,11 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                      int *counters, int *status) {
     constexpr int B_BYTES = NTOK * 128;
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((128u >> 4) << 24);
-    constexpr uint32_t TMEM_COLS = NTOK == 16 ? 128u : 256u;  // DG_ACC x (D, S)
+    constexpr uint32_t TMEM_COLS = NTOK == 16 ? 64u : 128u;  // DG_ACC accumulators of NTOK columns
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *a_st = smem;                                   // [DG_STAGES][DG_A_BYTES]
-    uint8_t *ones = a_st + DG_STAGES * DG_A_BYTES;          // [128][64] bf16 1.0
-    uint8_t *b_st = ones + DG_ONES_BYTES;                      // [DG_XSTAGES][B_BYTES]
+    uint8_t *b_st = a_st + DG_STAGES * DG_A_BYTES;          // [DG_XSTAGES][B_BYTES]
     uint8_t *w_ring = b_st + DG_XSTAGES * B_BYTES;           // [4][DG_WSLOTS][DG_WSLOT_BYTES]
     DgShared *sh = (DgShared *)(w_ring + 4 * DG_WSLOTS * DG_WSLOT_BYTES);
 
@@ -142,8 +143,6 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         sh->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    for (int i = threadIdx.x; i < DG_ONES_BYTES / 4; i += DG_THREADS) reinterpret_cast<uint32_t *>(ones)[i] = 0x3F803F80u;
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     if (warp == 1) {  // tensor-memory allocation is a whole-warp operation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(sptr(&sh->tmem_base)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
@@ -179,7 +178,7 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             const int ab = use % DG_ACC;
             if (!bar_wait(&sh->accempty[ab], ((use / DG_ACC) & 1) ^ 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const uint32_t td = tmem + (uint32_t)(ab * 2 * NTOK), ts = td + (uint32_t)NTOK;
+            const uint32_t td = tmem + (uint32_t)(ab * NTOK);
             for (int half = 0; half < 2 && !*failed; ++half) {
                 const uint32_t suse = 2 * use + half;
                 const int s = suse % DG_STAGES, xs = suse % DG_XSTAGES;
@@ -187,12 +186,10 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                 if (!bar_wait(&sh->afull[s], (suse / DG_STAGES) & 1, failed)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 if (lane == 0) {
-                    const uint32_t a0 = sptr(a_st + s * DG_A_BYTES), b0 = sptr(b_st + xs * B_BYTES), o0 = sptr(ones);
+                    const uint32_t a0 = sptr(a_st + s * DG_A_BYTES), b0 = sptr(b_st + xs * B_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
+                    for (int k = 0; k < 4; ++k)
                         umma_bf16(td, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (half | k) != 0);
-                        umma_bf16(ts, umma_desc(o0 + k * 32), umma_desc(b0 + k * 32), IDESC, (half | k) != 0);
-                    }
                     umma_commit(&sh->sempty[s]);  // the operand stages are free when the MMAs retire
                     umma_commit(&sh->xempty[xs]);
                 }
@@ -236,7 +233,9 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             const uint32_t *bw = (const uint32_t *)(ring + ws * DG_WSLOT_BYTES) + (blk & 1) * W4_BLOCK_WORDS;
             const uint4 p0 = *reinterpret_cast<const uint4 *>(bw + r * 16 + half * 8);
             const uint4 p1 = *reinterpret_cast<const uint4 *>(bw + r * 16 + half * 8 + 4);
-            if (half == 0) sh->params[use % DG_PARAM_BUFS][t] = bw[256 + r];
+            const uint32_t pr = bw[256 + r];
+            if (half == 0) sh->params[use % DG_PARAM_BUFS][t] = pr;
+            const uint32_t nz2 = __byte_perm(pr, pr, 0x3232);  // bf16x2 -(128 + zero) of this channel
             bar_arrive(&sh->wempty[q][ws]);
             // refill the slot released one unit ago (both warps of the pair have read it by now, or will shortly)
             if (lane == 0 && use >= 1 && (int)use - 1 + DG_WSLOTS < n_units) {
@@ -255,7 +254,7 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             for (int c = 0; c < 8; ++c) {  // chunk c = 8 consecutive k = one code word
                 uint32_t o[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) o[j] = w4_pair_bf16(words[c], j, k_mask, k_magic);
+                for (int j = 0; j < 4; ++j) o[j] = bf16x2_add(w4_pair_bf16(words[c], j, k_mask, k_magic), nz2);  // q - zero, exact
                 *reinterpret_cast<uint4 *>(arow + ((c ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -275,18 +274,16 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             const int ab = use % DG_ACC;
             if (!bar_wait(&sh->accfull[ab], (use / DG_ACC) & 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t d[NTOK], sx[NTOK];
-            tmem_ld<NTOK>(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * 2 * NTOK), d);
-            tmem_ld<NTOK>(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * 2 * NTOK + NTOK), sx);
+            uint32_t d[NTOK];
+            tmem_ld<NTOK>(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * NTOK), d);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             const uint32_t pr = sh->params[use % DG_PARAM_BUFS][row];
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) bar_arrive(&sh->accempty[ab]);
-            const float sc = __uint_as_float(pr << 16), nz = __uint_as_float(pr & 0xffff0000u);
+            const float sc = __uint_as_float(pr << 16);
 #pragma unroll
-            for (int j = 0; j < NTOK; ++j)
-                acc[j] = fmaf(sc, fmaf(nz, __uint_as_float(sx[j]), __uint_as_float(d[j])), acc[j]);
+            for (int j = 0; j < NTOK; ++j) acc[j] = fmaf(sc, __uint_as_float(d[j]), acc[j]);
 
             if (g != G - 1 && u + 1 != rg.u1) continue;
             // ---- end of this CTA's share of channel tile nt
@@ -365,7 +362,7 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
 
 template <int NTOK>
 constexpr size_t dg_smem_bytes() {
-    return 1024 + DG_STAGES * DG_A_BYTES + DG_ONES_BYTES + DG_XSTAGES * NTOK * 128 + 4 * DG_WSLOTS * DG_WSLOT_BYTES + sizeof(DgShared);
+    return 1024 + DG_STAGES * DG_A_BYTES + DG_XSTAGES * NTOK * 128 + 4 * DG_WSLOTS * DG_WSLOT_BYTES + sizeof(DgShared);
 }
 
 template <int NTOK, int EPI>
