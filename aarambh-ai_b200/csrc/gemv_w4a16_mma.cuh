@@ -84,10 +84,14 @@ __device__ __forceinline__ unsigned long long mbar_wall_ns() {
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
     if (mbar_try_wait(addr, parity)) return true;
-    const unsigned long long t0 = mbar_wall_ns();
+    unsigned long long t0 = 0;  // read only once a wait has lasted: the timer is a slow register
     for (int spin = 0;; ++spin) {
         if (mbar_try_wait(addr, parity)) return true;
-        if ((spin & 15) == 15 && mbar_wall_ns() - t0 > 2000000000ull) return false;
+        if ((spin & 31) == 31) {
+            const unsigned long long now = mbar_wall_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) return false;
+        }
     }
 }
 // global -> shared bulk copy (16-byte aligned, size a multiple of 16), completion

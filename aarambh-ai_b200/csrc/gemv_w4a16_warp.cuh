@@ -102,10 +102,14 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
 // one instruction.
 __device__ __forceinline__ uint32_t mbar_wait_addr(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return 1u;
-    const unsigned long long t0 = mbar_wall_ns();
+    unsigned long long t0 = 0;  // read only once a wait has lasted: the timer is a slow register
     for (int spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return 1u;
-        if ((spin & 15) == 15 && mbar_wall_ns() - t0 > 2000000000ull) return 0u;
+        if ((spin & 31) == 31) {
+            const unsigned long long now = mbar_wall_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) return 0u;
+        }
     }
 }
 

@@ -40,10 +40,11 @@ __device__ __forceinline__ bool bar_wait(uint64_t *b, uint32_t parity, volatile 
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if (spin == 0) t0 = wall_ns();
-        if ((spin & 15) == 15) {
+        if ((spin & 31) == 31) {  // the timer is a slow register: read only once a wait has lasted
             if (*failed) return false;
-            if (wall_ns() - t0 > 2000000000ull) break;
+            const unsigned long long now = wall_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) break;
         }
     }
     *failed = 1;
