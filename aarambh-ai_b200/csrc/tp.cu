@@ -91,7 +91,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 // One CTA.  The partial sums of exchange e = epoch + 1 sit in buffer e & 1 of
 // every inbox (stored there by the projection kernels that ran before this one
 // on each rank).  x += bf16(sum_r partial_r), summed in rank order on every rank.
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc *desc, int *status) {
     __shared__ int failed;
     pdl_wait();  // this rank's partial sums (and x) come from the preceding kernels
@@ -100,38 +100,88 @@ tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc
     const uint32_t e = *d.epoch + 1;
     if (threadIdx.x == 0) failed = 0;
     __syncthreads();
-    if ((int)threadIdx.x < d.world && (int)threadIdx.x != d.rank) {
-        const int p = threadIdx.x;
-        __threadfence_system();
-        st_release_sys(d.flags[p] + d.rank, e);  // "my partial sums of exchange e are in your inbox"
-        const uint32_t *mine = d.flags[d.rank] + p;
-        bool ok = false;
-        unsigned long long t0, now;
-        asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
-        for (int spin = 0;; ++spin) {
-            // the count only grows; a peer that is ahead has already passed e
-            if ((int32_t)(ld_acquire_sys(mine) - e) >= 0) { ok = true; break; }
-            if ((spin & 63) == 63) {
-                asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-                if (now - t0 > 2000000000ull) break;  // two seconds
+    // CTA 0 exchanges the arrival signals with the peers and publishes the outcome in a local
+    // word; the other CTAs (a few, all resident at once) wait for that word.
+    if (blockIdx.x == 0) {
+        if ((int)threadIdx.x < d.world && (int)threadIdx.x != d.rank) {
+            const int p = threadIdx.x;
+            __threadfence_system();
+            st_release_sys(d.flags[p] + d.rank, e);  // "my partial sums of exchange e are in your inbox"
+            const uint32_t *mine = d.flags[d.rank] + p;
+            bool ok = false;
+            unsigned long long t0, now;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+            for (int spin = 0;; ++spin) {
+                // the count only grows; a peer that is ahead has already passed e
+                if ((int32_t)(ld_acquire_sys(mine) - e) >= 0) { ok = true; break; }
+                if ((spin & 63) == 63) {
+                    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+                    if (now - t0 > 2000000000ull) break;  // two seconds
+                }
+                __nanosleep(20);
             }
-            __nanosleep(20);
+            if (!ok) failed = 1;
         }
-        if (!ok) failed = 1;
+        __syncthreads();
+        if (threadIdx.x == 0 && !failed)
+            asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(d.ready), "r"(e) : "memory");
+    } else {
+        if (threadIdx.x == 0) {
+            bool ok = false;
+            unsigned long long t0, now;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+            for (int spin = 0;; ++spin) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(d.ready) : "memory");
+                if ((int32_t)(v - e) >= 0) { ok = true; break; }
+                if ((spin & 63) == 63) {
+                    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+                    if (now - t0 > 3000000000ull) break;  // CTA 0's own limit plus a margin
+                }
+                __nanosleep(20);
+            }
+            if (!ok) failed = 1;
+        }
+        __syncthreads();
     }
-    __syncthreads();
     if (failed) {
         if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
         return;
     }
     const float *box = d.inbox[d.rank] + (size_t)(e & 1u) * d.world * d.max_elems;
-    for (size_t i = threadIdx.x; i < count; i += blockDim.x) {
-        float sum = 0.f;
-        for (int r = 0; r < d.world; ++r) sum += __ldcg(box + (size_t)r * d.max_elems + i);
-        x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(__float2bfloat16_rn(sum)));
+    const size_t nvec = count >> 3;  // 8 elements per thread and pass
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < d.world; ++r) {
+            const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)r * d.max_elems) + 2 * i);
+            const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)r * d.max_elems) + 2 * i + 1);
+            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
+            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+        }
+        const uint4 xv = reinterpret_cast<const uint4 *>(x)[i];
+        uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f0 = __uint_as_float(w[j] << 16) + __bfloat162float(__float2bfloat16_rn(sum[2 * j]));
+            const float f1 = __uint_as_float(w[j] & 0xffff0000u) + __bfloat162float(__float2bfloat16_rn(sum[2 * j + 1]));
+            w[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f0)) |
+                   ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f1)) << 16);
+        }
+        reinterpret_cast<uint4 *>(x)[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    if (blockIdx.x == 0)  // a tail of fewer than 8 elements
+        for (size_t i = (nvec << 3) + threadIdx.x; i < count; i += blockDim.x) {
+            float sum = 0.f;
+            for (int r = 0; r < d.world; ++r) sum += __ldcg(box + (size_t)r * d.max_elems + i);
+            x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(__float2bfloat16_rn(sum)));
+        }
     __syncthreads();
-    if (threadIdx.x == 0) *d.epoch = e;
+    // every CTA has read the exchange count and its share of the inbox: the last one closes the exchange
+    if (threadIdx.x == 0 && atomicAdd(d.done, 1u) == gridDim.x - 1) {
+        *d.done = 0;
+        __threadfence();
+        *d.epoch = e;
+    }
 }
 
 }  // namespace
@@ -145,7 +195,9 @@ int tp_peer_reduce_add(ab2_tp *tp, void *x_bf16, size_t count, cudaStream_t s) {
     int *status = nullptr;
     int rc = device_status_word(&status);
     if (rc != AB2_OK) return rc;
-    cudaError_t e = launch_kernel(tp_peer_reduce_add_kernel, dim3(1), dim3(1024), 0, s, (__nv_bfloat16 *)x_bf16, count,
+    AB2_REQUIRE(((uintptr_t)x_bf16 & 15) == 0, AB2_ERR_BAD_ALIGN, "the residual stream must be 16-byte aligned");
+    const unsigned ctas = (unsigned)std::max<size_t>(1, std::min<size_t>(32, (count / 8 + 255) / 256));
+    cudaError_t e = launch_kernel(tp_peer_reduce_add_kernel, dim3(ctas), dim3(256), 0, s, (__nv_bfloat16 *)x_bf16, count,
                                   (const ab2_tp_peer_desc *)tp->desc_dev, status);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "peer reduce launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;

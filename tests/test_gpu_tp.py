@@ -1,7 +1,8 @@
 """Tensor-parallel decoder against the single-GPU decoder (needs 2 GPUs; skipped
 otherwise): same seeded weights, sharded over 2 ranks, logits within 1e-2
 relative and the same greedy tokens - once with the partial sums exchanged over
-NVLink peer memory, once through NCCL; plain launches and graph-replayed steps."""
+NVLink peer memory, once through NCCL; plain launches, graph-replayed steps and
+three rows decoded together."""
 import os
 import socket
 
@@ -69,6 +70,18 @@ def _run(model, steps=6):
         lg = out.float().cpu().numpy().ravel()
         logits.append(lg)
         toks.append(int(np.argmax(lg)))
+    # three rows decoded together (2..16 tokens per step: the stand-alone reduce over the inboxes)
+    rows = 3
+    bcache = model.empty_kv_cache_with_capacity(32, batch=rows, dtype="int8")
+    for b in range(rows):
+        model.forward_with_cache(ids[:, :3 + b], 0, bcache, row=b, last_only=True)
+    bout = torch.empty((rows, CFG["vocab"]), dtype=torch.bfloat16, device="cuda")
+    btok = torch.tensor([11, 600, 1999], dtype=torch.int32, device="cuda")
+    for i in range(3):
+        with torch.cuda.stream(side):
+            model.decode_step(btok, bcache, bout, None)
+            side.synchronize()
+        logits.extend(bout.float().cpu().numpy())
     return np.stack(logits), toks
 
 
