@@ -226,6 +226,8 @@ __global__ void __launch_bounds__(128) attn_split_kernel(AttnArgs a) {
 
 // Log-sum-exp merge of the context splits: grid (h, nrows), HD threads.
 __global__ void attn_merge_kernel(AttnArgs a, int HD) {
+    pdl_wait();  // inputs come from the preceding kernel of the step
+    pdl_launch_dependents();
     const int head = blockIdx.x, rrow = blockIdx.y, row = a.row0 + rrow, d = threadIdx.x;
     const size_t p0 = ((size_t)row * a.h + head) * a.nsplit;
     float M = -INFINITY;
@@ -281,8 +283,10 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
         int rc = attention_decode_mma_device(kv, layer, q, out, row0, nrows, scale, dtype, nsplit, kv->part_acc,
                                              kv->part_ml, pending, st.q_b, s);
         if (rc != AB2_OK) return rc;
-        if (nsplit > 1) attn_merge_kernel<<<dim3(kv->h, nrows), kv->hd, 0, s>>>(a, kv->hd);
-        AB2_LAUNCH_CHECK();
+        if (nsplit > 1) {
+            cudaError_t e = launch_kernel(attn_merge_kernel, dim3(kv->h, nrows), dim3(kv->hd), 0, s, a, (int)kv->hd);
+            if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "attention merge launch failed: %s", cudaGetErrorString(e));
+        }
         return AB2_OK;
     }
     if (S == 1) {

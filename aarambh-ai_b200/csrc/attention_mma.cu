@@ -74,6 +74,8 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(MmaAttnArgs a) {
     __shared__ alignas(128) uint8_t vst[4][2][16 * HD];  // per warp, double-buffered V block (swizzled 16-byte chunks)
     __shared__ float wm[4][8], wl[4][8];
     __shared__ float wacc[4][8][HD];
+    pdl_wait();  // inputs come from the preceding kernel of the step
+    pdl_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int split = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = a.row0 + rrow;
@@ -275,8 +277,8 @@ int attention_decode_mma_device(const ab2_kv *kv, int layer, const void *q, void
     a.q = q; a.out = out; a.row0 = row0; a.h = kv->h; a.rep = kv->h / kv->kvh; a.nsplit = nsplit;
     a.dtype = (int)dtype; a.scale = scale; a.part_acc = part_acc; a.part_ml = part_ml;
     a.pending = pending; a.q_stride = q_stride;
-    attn_decode_mma_kernel<<<dim3(nsplit, kv->kvh, nrows), 128, 0, s>>>(a);
-    AB2_LAUNCH_CHECK();
+    cudaError_t e = launch_kernel(attn_decode_mma_kernel, dim3(nsplit, kv->kvh, nrows), dim3(128), 0, s, a);
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "decode attention launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 

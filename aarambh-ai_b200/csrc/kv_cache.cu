@@ -30,6 +30,8 @@ __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T 
                                  long long in_stride, int S, int row0, const float *__restrict__ cos_t,
                                  const float *__restrict__ sin_t, const int *__restrict__ rope_pos) {
     extern __shared__ float sh[];  // [2][hd] values, then 2 * 8 reduction slots
+    pdl_wait();  // inputs come from the preceding kernel of the step
+    pdl_launch_dependents();
     const int hd = kv.hd, half = hd >> 1;
     const int s = blockIdx.x, head = blockIdx.y, rrow = blockIdx.z, row = row0 + rrow;
     const int d = threadIdx.x;
@@ -135,13 +137,14 @@ static int launch_append(ab2_kv *kv, int layer, const T *k, const T *v, long lon
     KvView view = kv_view(kv, layer);
     dim3 grid(S, kv->kvh, nrows);
     size_t smem = (2 * (size_t)kv->hd + 16) * sizeof(float);
+    cudaError_t e;
     if (kv->dtype == AB2_KV_F32)
-        kv_append_kernel<T, AB2_KV_F32><<<grid, kv->hd, smem, s>>>(view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_F32>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
     else if (kv->dtype == AB2_KV_BF16)
-        kv_append_kernel<T, AB2_KV_BF16><<<grid, kv->hd, smem, s>>>(view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_BF16>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
     else
-        kv_append_kernel<T, AB2_KV_INT8><<<grid, kv->hd, smem, s>>>(view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
-    AB2_LAUNCH_CHECK();
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_INT8>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "KV append launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 

@@ -72,6 +72,8 @@ template <typename T>
 __global__ void rope_q_kernel(T *qkv, long long stride, int heads, int hd, int S, int row0,
                               const int *__restrict__ base, const float *__restrict__ cos_t,
                               const float *__restrict__ sin_t, size_t total_pairs) {
+    pdl_wait();  // inputs come from the preceding kernel of the step
+    pdl_launch_dependents();
     const int half = hd >> 1;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total_pairs) return;
@@ -104,6 +106,8 @@ __global__ void add_f32_projection_kernel(__nv_bfloat16 *x, const float *p, size
 // SwiGLU over the output of the interleaved gate|up weight: columns come in
 // blocks of 16 = 8 gate values followed by the 8 matching up values.
 __global__ void swiglu_interleaved8_kernel(const __nv_bfloat16 *gu, __nv_bfloat16 *out, int ffn, size_t n) {
+    pdl_wait();  // inputs come from the preceding kernel of the step
+    pdl_launch_dependents();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     size_t tok = i / ffn;
@@ -129,12 +133,13 @@ static int launch_rope_q(ab2_model *m, int T, int S, int row0, const int *base, 
     long long stride = (long long)(c.n_heads + 2 * c.n_kv_heads) * c.head_dim;
     size_t pairs = (size_t)T * c.n_heads * (c.head_dim / 2);
     unsigned blocks = (unsigned)ceil_div(pairs, 256);
+    cudaError_t e;
     switch (m->dtype) {
-    case AB2_F32: rope_q_kernel<float><<<blocks, 256, 0, s>>>((float *)m->qkv, stride, c.n_heads, c.head_dim, S, row0, base, m->cos_t, m->sin_t, pairs); break;
-    case AB2_F16: rope_q_kernel<__half><<<blocks, 256, 0, s>>>((__half *)m->qkv, stride, c.n_heads, c.head_dim, S, row0, base, m->cos_t, m->sin_t, pairs); break;
-    default: rope_q_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16 *)m->qkv, stride, c.n_heads, c.head_dim, S, row0, base, m->cos_t, m->sin_t, pairs); break;
+    case AB2_F32: e = launch_kernel(rope_q_kernel<float>, dim3(blocks), dim3(256), 0, s, (float *)m->qkv, stride, (int)c.n_heads, (int)c.head_dim, S, row0, base, (const float *)m->cos_t, (const float *)m->sin_t, pairs); break;
+    case AB2_F16: e = launch_kernel(rope_q_kernel<__half>, dim3(blocks), dim3(256), 0, s, (__half *)m->qkv, stride, (int)c.n_heads, (int)c.head_dim, S, row0, base, (const float *)m->cos_t, (const float *)m->sin_t, pairs); break;
+    default: e = launch_kernel(rope_q_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16 *)m->qkv, stride, (int)c.n_heads, (int)c.head_dim, S, row0, base, (const float *)m->cos_t, (const float *)m->sin_t, pairs); break;
     }
-    AB2_LAUNCH_CHECK();
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "RoPE launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 
@@ -274,8 +279,9 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
             {
                 size_t n = (size_t)T * c.ffn_hidden;
-                swiglu_interleaved8_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, s>>>((const __nv_bfloat16 *)m->gu, (__nv_bfloat16 *)m->hid, c.ffn_hidden, n);
-                AB2_LAUNCH_CHECK();
+                cudaError_t e = launch_kernel(swiglu_interleaved8_kernel, dim3((unsigned)ceil_div(n, 256)), dim3(256), 0, s,
+                                              (const __nv_bfloat16 *)m->gu, (__nv_bfloat16 *)m->hid, (int)c.ffn_hidden, n);
+                if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "SwiGLU launch failed: %s", cudaGetErrorString(e));
             }
             STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
             STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));

@@ -158,6 +158,8 @@ __global__ void swiglu_fused_kernel(const T *__restrict__ gu, T *out, int ffn, s
 
 template <typename T>
 __global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *out, size_t n) {
+    pdl_wait();  // inputs come from the preceding kernel of the step
+    pdl_launch_dependents();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = from_f32<T>(__fadd_rn(to_f32(a[i]), to_f32(b[i])));
 }
@@ -176,12 +178,13 @@ int launch_swiglu_fused(const void *gu, void *out, int tokens, int ffn, ab2_dtyp
 
 int launch_add(const void *a, const void *b, void *out, size_t n, ab2_dtype dtype, cudaStream_t s) {
     unsigned blocks = (unsigned)ceil_div(n, 256);
+    cudaError_t e;
     switch (dtype) {
-    case AB2_F32: add_kernel<float><<<blocks, 256, 0, s>>>((const float *)a, (const float *)b, (float *)out, n); break;
-    case AB2_F16: add_kernel<__half><<<blocks, 256, 0, s>>>((const __half *)a, (const __half *)b, (__half *)out, n); break;
-    default: add_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)out, n); break;
+    case AB2_F32: e = launch_kernel(add_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float *)a, (const float *)b, (float *)out, n); break;
+    case AB2_F16: e = launch_kernel(add_kernel<__half>, dim3(blocks), dim3(256), 0, s, (const __half *)a, (const __half *)b, (__half *)out, n); break;
+    default: e = launch_kernel(add_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16 *)a, (const __nv_bfloat16 *)b, (__nv_bfloat16 *)out, n); break;
     }
-    AB2_LAUNCH_CHECK();
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "add launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 
