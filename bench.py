@@ -210,6 +210,7 @@ def cpu_decode_baseline(pkg, torch, weights, cfg, steps, warmup, ctx):
     for name, w in weights.items():
         dense[name] = (w.dequantise(torch.float32) if hasattr(w, "dequantise") else w.float()).cpu().numpy()
     c = dict(cfg, eps=1e-5, rope_theta=10000.0)
+    orc.use_all_cores()  # torchrun exports OMP_NUM_THREADS=1 to its workers
     model = orc.DenseModel(c, dense, 1, ctx + steps + warmup + 1)
     model.fill_cache(0, ctx, 1)
     tok = np.array([[17]], np.uint32)

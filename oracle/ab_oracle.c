@@ -45,6 +45,16 @@ ORC_API int orc_num_threads(void) {
 #endif
 }
 
+/* Thread count of the parallel loops (a launcher may have exported
+ * OMP_NUM_THREADS=1 for its worker processes). */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* Rust `x as i8` / `x as u8` after clamp: saturating, NaN -> 0
  * (crates/aarambh-studio-quant/src/absmax.rs:17, int4.rs:31). */
 static inline int8_t cast_i8(float v) {

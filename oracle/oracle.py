@@ -49,6 +49,7 @@ _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 
 def _declare(L):
     L.orc_num_threads.restype = C.c_int
+    L.orc_set_threads.argtypes = [C.c_int]; L.orc_set_threads.restype = None
     L.orc_f32_to_f16.argtypes = [C.c_float]; L.orc_f32_to_f16.restype = C.c_uint16
     L.orc_f32_to_f16_rne.argtypes = [C.c_float]; L.orc_f32_to_f16_rne.restype = C.c_uint16
     L.orc_f16_to_f32.argtypes = [C.c_uint16]; L.orc_f16_to_f32.restype = C.c_float
@@ -102,6 +103,15 @@ def _f32(a):
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+def use_all_cores() -> int:
+    """Runs the parallel loops on every core this process may use (a launcher
+    such as torchrun exports OMP_NUM_THREADS=1 to its workers); returns the count."""
+    import os
+    n = len(os.sched_getaffinity(0))
+    lib().orc_set_threads(n)
+    return num_threads()
 
 
 # --- f16 / bf16 -------------------------------------------------------------
