@@ -28,13 +28,26 @@ static size_t kv_elem_size(int dtype) { return dtype == AB2_KV_F32 ? 4 : dtype =
 template <typename T, int KVD>
 __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T *__restrict__ v_in,
                                  long long in_stride, int S, int row0, const float *__restrict__ cos_t,
-                                 const float *__restrict__ sin_t, const int *__restrict__ rope_pos) {
+                                 const float *__restrict__ sin_t, const int *__restrict__ rope_pos,
+                                 T *q_rot, int q_heads) {
     extern __shared__ float sh[];  // [2][hd] values, then 2 * 8 reduction slots
     pdl_wait();  // inputs come from the preceding kernel of the step
     pdl_launch_dependents();
     const int hd = kv.hd, half = hd >> 1;
     const int s = blockIdx.x, head = blockIdx.y, rrow = blockIdx.z, row = row0 + rrow;
     const int d = threadIdx.x;
+    if (head >= kv.kvh) {
+        // blocks past the KV heads rotate one query head in place (same row stride as k / v)
+        T *q = q_rot + ((size_t)rrow * S + s) * (size_t)in_stride + (size_t)(head - kv.kvh) * hd;
+        sh[d] = to_f32(q[d]);
+        __syncthreads();
+        const int p = (rope_pos ? rope_pos[row] : kv.lens[row]) + s;
+        const int i = d < half ? d : d - half;
+        float o1, o2;
+        rope_rotate(sh[i], sh[half + i], cos_t[(size_t)p * half + i], sin_t[(size_t)p * half + i], o1, o2);
+        q[d] = from_f32<T>(d < half ? o1 : o2);
+        return;
+    }
     const int pos = kv.lens[row] + s;
     if (pos >= kv.cap) return;  // capacity is checked on the host; never write out of range
     const size_t in_off = ((size_t)rrow * S + s) * (size_t)in_stride + (size_t)head * hd;
@@ -133,28 +146,29 @@ KvView kv_view(const ab2_kv *kv, int layer) {
 template <typename T>
 static int launch_append(ab2_kv *kv, int layer, const T *k, const T *v, long long in_stride, int S,
                          int row0, int nrows, const float *cos_t, const float *sin_t,
-                         const int *rope_pos, cudaStream_t s) {
+                         const int *rope_pos, T *q_rot, int q_heads, cudaStream_t s) {
     KvView view = kv_view(kv, layer);
-    dim3 grid(S, kv->kvh, nrows);
+    if (q_rot == nullptr || cos_t == nullptr) q_heads = 0;
+    dim3 grid(S, kv->kvh + q_heads, nrows);
     size_t smem = (2 * (size_t)kv->hd + 16) * sizeof(float);
     cudaError_t e;
     if (kv->dtype == AB2_KV_F32)
-        e = launch_kernel(kv_append_kernel<T, AB2_KV_F32>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_F32>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads);
     else if (kv->dtype == AB2_KV_BF16)
-        e = launch_kernel(kv_append_kernel<T, AB2_KV_BF16>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_BF16>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads);
     else
-        e = launch_kernel(kv_append_kernel<T, AB2_KV_INT8>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_INT8>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "KV append launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 
 int kv_append_device(ab2_kv *kv, int layer, const void *k, const void *v, long long in_stride, int S,
                      int row0, int nrows, ab2_dtype dtype, const float *cos_t, const float *sin_t,
-                     const int *rope_pos, cudaStream_t s) {
+                     const int *rope_pos, cudaStream_t s, void *q_rot, int q_heads) {
     switch (dtype) {
-    case AB2_F32: return launch_append<float>(kv, layer, (const float *)k, (const float *)v, in_stride, S, row0, nrows, cos_t, sin_t, rope_pos, s);
-    case AB2_F16: return launch_append<__half>(kv, layer, (const __half *)k, (const __half *)v, in_stride, S, row0, nrows, cos_t, sin_t, rope_pos, s);
-    default: return launch_append<__nv_bfloat16>(kv, layer, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, in_stride, S, row0, nrows, cos_t, sin_t, rope_pos, s);
+    case AB2_F32: return launch_append<float>(kv, layer, (const float *)k, (const float *)v, in_stride, S, row0, nrows, cos_t, sin_t, rope_pos, (float *)q_rot, q_heads, s);
+    case AB2_F16: return launch_append<__half>(kv, layer, (const __half *)k, (const __half *)v, in_stride, S, row0, nrows, cos_t, sin_t, rope_pos, (__half *)q_rot, q_heads, s);
+    default: return launch_append<__nv_bfloat16>(kv, layer, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, in_stride, S, row0, nrows, cos_t, sin_t, rope_pos, (__nv_bfloat16 *)q_rot, q_heads, s);
     }
 }
 

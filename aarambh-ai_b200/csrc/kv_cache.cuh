@@ -32,9 +32,11 @@ KvView kv_view(const ab2_kv *kv, int layer);
 
 // Writes S tokens per row at the rows' current lengths (no advance).  k / v
 // element (row, s, head, d) sits at (row * S + s) * in_stride + head * hd + d.
+// With `q_rot` (rows of the same stride, `q_heads` heads of hd) the same launch
+// rotates the query heads in place.
 int kv_append_device(ab2_kv *kv, int layer, const void *k, const void *v, long long in_stride, int S,
                      int row0, int nrows, ab2_dtype dtype, const float *cos_t, const float *sin_t,
-                     const int *rope_pos, cudaStream_t s);
+                     const int *rope_pos, cudaStream_t s, void *q_rot = nullptr, int q_heads = 0);
 int kv_commit_device(ab2_kv *kv, int S, int row0, int nrows, cudaStream_t s);
 
 // Attention of S new queries per row over the cache.  `pending` is the number of

@@ -66,29 +66,6 @@ struct ab2_model {
 
 namespace ab2 {
 
-// Rotates the query part of the fused QKV activations in place.
-// qkv [tokens][stride]; token t = row * S + s uses position base[row0 + row] + s.
-template <typename T>
-__global__ void rope_q_kernel(T *qkv, long long stride, int heads, int hd, int S, int row0,
-                              const int *__restrict__ base, const float *__restrict__ cos_t,
-                              const float *__restrict__ sin_t, size_t total_pairs) {
-    pdl_wait();  // inputs come from the preceding kernel of the step
-    pdl_launch_dependents();
-    const int half = hd >> 1;
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total_pairs) return;
-    int i = (int)(idx % half);
-    size_t th = idx / half;
-    int head = (int)(th % heads);
-    size_t tok = th / heads;
-    int pos = base[row0 + (int)(tok / S)] + (int)(tok % S);
-    T *p = qkv + tok * stride + (size_t)head * hd;
-    float o1, o2;
-    rope_rotate(to_f32(p[i]), to_f32(p[half + i]), cos_t[(size_t)pos * half + i], sin_t[(size_t)pos * half + i], o1, o2);
-    p[i] = from_f32<T>(o1);
-    p[half + i] = from_f32<T>(o2);
-}
-
 // Copies the last token's row of every sequence: in [nrows][S][d] -> out [nrows][d].
 template <typename T>
 __global__ void gather_last_kernel(const T *in, T *out, int S, int d) {
@@ -126,21 +103,6 @@ __global__ void reorder_shards_kernel(const T *in, T *out, int rows, int vn, int
     int r = (int)((i / vn) % world);
     int b = (int)(i / ((size_t)vn * world));
     out[i] = in[((size_t)r * rows + b) * vn + j];
-}
-
-static int launch_rope_q(ab2_model *m, int T, int S, int row0, const int *base, cudaStream_t s) {
-    const ab2_model_config &c = m->cfg;
-    long long stride = (long long)(c.n_heads + 2 * c.n_kv_heads) * c.head_dim;
-    size_t pairs = (size_t)T * c.n_heads * (c.head_dim / 2);
-    unsigned blocks = (unsigned)ceil_div(pairs, 256);
-    cudaError_t e;
-    switch (m->dtype) {
-    case AB2_F32: e = launch_kernel(rope_q_kernel<float>, dim3(blocks), dim3(256), 0, s, (float *)m->qkv, stride, (int)c.n_heads, (int)c.head_dim, S, row0, base, (const float *)m->cos_t, (const float *)m->sin_t, pairs); break;
-    case AB2_F16: e = launch_kernel(rope_q_kernel<__half>, dim3(blocks), dim3(256), 0, s, (__half *)m->qkv, stride, (int)c.n_heads, (int)c.head_dim, S, row0, base, (const float *)m->cos_t, (const float *)m->sin_t, pairs); break;
-    default: e = launch_kernel(rope_q_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16 *)m->qkv, stride, (int)c.n_heads, (int)c.head_dim, S, row0, base, (const float *)m->cos_t, (const float *)m->sin_t, pairs); break;
-    }
-    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "RoPE launch failed: %s", cudaGetErrorString(e));
-    return AB2_OK;
 }
 
 // Decode attention as rotation + append + tensor-core flash-decode (+ merge) instead of the
@@ -215,11 +177,11 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
                                                    m->cos_t, m->sin_t, rope_base == kv->lens_dev ? nullptr : rope_base,
                                                    len_hint, s));
         } else {
-            STEP(launch_rope_q(m, T, S, row0, rope_base, s));
+            // one launch: RoPE on the query heads in place, RoPE + quantise + append of K / V
             const char *kptr = (const char *)m->qkv + (size_t)c.n_heads * hd * esz;
             const char *vptr = kptr + (size_t)c.n_kv_heads * hd * esz;
             STEP(kv_append_device(kv, l, kptr, vptr, qkv_stride, S, row0, nrows, m->dtype, m->cos_t, m->sin_t,
-                                  rope_base == kv->lens_dev ? nullptr : rope_base, s));
+                                  rope_base == kv->lens_dev ? nullptr : rope_base, s, m->qkv, c.n_heads));
             AttnStrides st;
             st.q_h = hd; st.q_s = qkv_stride; st.q_b = qkv_stride * S;
             st.o_h = hd; st.o_s = (long long)c.n_heads * hd; st.o_b = st.o_s * S;
