@@ -262,6 +262,26 @@ static int launch_split_hd(const AttnArgs &a, dim3 grid, cudaStream_t s) {
     return AB2_OK;
 }
 
+int device_sm_count();
+
+// Whether decode queries over this cache take the tensor-core flash-decode (attention_mma.cu).
+static bool decode_on_mma(const ab2_kv *kv) {
+    return kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8;
+}
+
+// Context splits of a decode launch over `nrows` sequences of at most `max_len` tokens: enough
+// CTAs to fill the GPU a few times over, never a split shorter than a useful run of tokens.
+// One rule for every entry point, so that they return the same bits.
+static int decode_split_count(const ab2_kv *kv, int nrows, int max_len, int max_splits, bool mma) {
+    const int sms = device_sm_count(), units = nrows * kv->kvh;
+    if (mma) {
+        const int want = (sms * 6 + units - 1) / units;
+        return std::max(1, std::min(std::min(want, (max_len + 63) / 64), max_splits));
+    }
+    const int want = (2 * sms + units - 1) / units;
+    return std::max(1, std::min(std::min(want, (max_len + 255) / 256), max_splits));
+}
+
 int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *out, int S, int pending,
                             int row0, int nrows, float scale, ab2_dtype dtype, AttnStrides st,
                             int len_hint, cudaStream_t s) {
@@ -274,11 +294,9 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
     if (max_len <= 0)
         for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + pending);
     int nsplit = 1;
-    if (S == 1 && kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8 &&
-        st.q_h == kv->hd && st.o_h == st.q_h && st.o_b == (long long)kv->h * kv->hd) {
+    if (S == 1 && decode_on_mma(kv) && st.q_h == kv->hd && st.o_h == st.q_h && st.o_b == (long long)kv->h * kv->hd) {
         // INT8 cache, head_dim 128: tensor-core flash-decode (attention_mma.cu)
-        const int want = (148 * 6 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
-        nsplit = std::max(1, std::min(std::min(want, (max_len + 63) / 64), kv->max_splits));
+        nsplit = decode_split_count(kv, nrows, max_len, kv->max_splits, true);
         a.nsplit = nsplit;
         int rc = attention_decode_mma_device(kv, layer, q, out, row0, nrows, scale, dtype, nsplit, kv->part_acc,
                                              kv->part_ml, pending, st.q_b, s);
@@ -289,11 +307,7 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
         }
         return AB2_OK;
     }
-    if (S == 1) {
-        int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
-        int by_len = (max_len + 255) / 256;
-        nsplit = std::max(1, std::min(std::min(want, by_len), kv->max_splits));
-    }
+    if (S == 1) nsplit = decode_split_count(kv, nrows, max_len, kv->max_splits, false);
     a.nsplit = nsplit;
     dim3 grid(nsplit, kv->kvh, nrows * S);
     int rc;
@@ -419,16 +433,10 @@ AB2_API int ab2_attention_decode_static(const ab2_kv *kv, int layer, const void 
     a.st.o_b = a.st.q_b; a.st.o_s = 0; a.st.o_h = kv->hd;
     int max_len = 0;
     for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r]);
-    // Same kernel choice and split count as ab2_attention_decode, so both entry
-    // points return the same bits.
-    const bool mma_path = kv->dtype == AB2_KV_INT8 && kv->hd == 128 && kv->h / kv->kvh <= 8;
-    if (mma_path) {
-        const int want = (148 * 6 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
-        a.nsplit = std::max(1, std::min(std::min(want, (max_len + 63) / 64), AB2_KV_MAX_SPLITS));
-    } else {
-        const int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
-        a.nsplit = std::max(1, std::min(std::min(want, (max_len + 255) / 256), AB2_KV_MAX_SPLITS));
-    }
+    // Kernel choice and split count come from the helpers ab2_attention_decode uses (with the
+    // cache's own split limit), so both entry points return the same bits.
+    const bool mma_path = decode_on_mma(kv);
+    a.nsplit = decode_split_count(kv, nrows, max_len, kv->max_splits, mma_path);
     // Partials are indexed by the absolute row, exactly as in the allocated scratch.
     const size_t parts = (size_t)(row0 + nrows) * kv->h * a.nsplit;
     const size_t need = parts * ((size_t)kv->hd + 2);

@@ -20,6 +20,7 @@
 using namespace ab2;
 
 namespace ab2 {
+int device_sm_count();
 namespace {
 
 __device__ __forceinline__ float ld_act(const void *p, int dtype, size_t i) {
@@ -447,7 +448,7 @@ int attention_decode_fused_device(ab2_kv *kv, int layer, const void *qkv, long l
     int max_len = len_hint;
     if (max_len <= 0)
         for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r]);
-    const int want = (2 * 148 + nrows * kv->kvh - 1) / (nrows * kv->kvh);
+    const int want = (2 * device_sm_count() + nrows * kv->kvh - 1) / (nrows * kv->kvh);
     a.nsplit = std::max(1, std::min(std::min(want, (max_len + 127) / 128), kv->max_splits));
     dim3 grid(a.nsplit, kv->kvh, nrows);
     int rc;

@@ -264,10 +264,13 @@ int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t 
     rc = make_x_map(&map, x, M, w->K, NTOK);
     if (rc != AB2_OK) return rc;
     const size_t smem = 1024 + TC_STAGES * TC_A_BYTES + tc_xstages<NTOK>() * NTOK * 128 + TC_WSLOTS * TC_WSLOT_BYTES + sizeof(TcShared);
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};  // the attribute is per device
+    int dev = 0;
+    AB2_CUDA(cudaGetDevice(&dev));
+    AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
+    if (!configured[dev]) {
         AB2_CUDA(cudaFuncSetAttribute(gemm_w4a16_tc_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
+        configured[dev] = true;
     }
     const int items = ((w->N + 127) / 128) * ((M + NTOK - 1) / NTOK);
     const int grid = std::min(items, device_sm_count());

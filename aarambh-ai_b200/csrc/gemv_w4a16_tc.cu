@@ -375,10 +375,13 @@ int launch_dg(const ab2_qweight *w, const void *x, int M, void *y, const void *r
     rc = make_x_map(&map, x, M, w->K, NTOK);
     if (rc != AB2_OK) return rc;
     const size_t smem = dg_smem_bytes<NTOK>();
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};  // the attribute is per device
+    int dev = 0;
+    AB2_CUDA(cudaGetDevice(&dev));
+    AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
+    if (!configured[dev]) {
         AB2_CUDA(cudaFuncSetAttribute(gemv_w4a16_tc_kernel<NTOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
+        configured[dev] = true;
     }
     const int units = ((w->N + 127) / 128) * (w->K / 128);
     const int grid = std::max(1, std::min(std::min(max_ctas, device_sm_count()), units / 2));

@@ -151,6 +151,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
     bool pending = false;
     const bool fuse_exchange = m->tp && m->tp->world > 1 && m->fused_epilogues && T == 1 &&
                                tp_peer_ready(m->tp, (size_t)d) && qlinear_w4a16_norm_fusable(m->layers[0].wqkv, m->dtype, T) &&
+                               qlinear_w4a16_norm_fusable(m->lm_head, m->dtype, T) &&  // it consumes the last exchange
                                getenv("AB2_TP_SEPARATE_REDUCE") == nullptr;
     auto consume = [&](const ab2_qweight *w, const float *norm_w, void *out, int epi) -> int {
         void *xnext = xcur == m->x ? m->xn : m->x;
@@ -407,8 +408,15 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
     AB2_REQUIRE(m->embedding && m->final_norm, AB2_ERR_BAD_ARG, "embedding or final norm not set");
     if (!m->lm_head) {
         AB2_REQUIRE(c.tied, AB2_ERR_BAD_ARG, "lm_head not set and embeddings are not tied");
+        // the tied head is the whole embedding table; a rank needs its own vocabulary shard
+        AB2_REQUIRE(!(m->tp && m->tp->world > 1), AB2_ERR_BAD_ARG,
+                    "tensor parallel needs an explicit lm_head shard of %d rows (tied embeddings are not sharded)",
+                    c.vocab / (m->tp ? m->tp->world : 1));
         m->lm_head = m->embedding;  // LmHead::tied_with_qat (crates/aarambh-studio-model/src/head.rs:59-64)
     }
+    if (m->tp && m->tp->world > 1)  // the context may have been set after the head
+        AB2_REQUIRE(m->lm_head->N == c.vocab / m->tp->world, AB2_ERR_BAD_SHAPE,
+                    "lm_head shard has %d rows, expected vocab / world = %d", m->lm_head->N, c.vocab / m->tp->world);
     bool fast = true;
     for (int l = 0; l < c.n_layers && fast; ++l)
         for (int i = 0; i < 7; ++i)
@@ -501,9 +509,11 @@ AB2_API int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev,
         if (!same) {
             // explicit seqlen offsets that differ from the cache lengths
             AB2_CUDA(cudaStreamSynchronize(s));
-            for (int r = 0; r < nrows; ++r) m->positions_host[row0 + r] = offsets_host[r];
-            AB2_CUDA(cudaMemcpyAsync(m->positions + row0, m->positions_host + row0, (size_t)nrows * 4, cudaMemcpyHostToDevice, s));
-            rope_base = m->positions;
+            // the buffers hold max_tokens entries and nrows <= max_tokens: they are filled from
+            // entry 0, and the kernels, which index by the absolute cache row, get the base moved back
+            for (int r = 0; r < nrows; ++r) m->positions_host[r] = offsets_host[r];
+            AB2_CUDA(cudaMemcpyAsync(m->positions, m->positions_host, (size_t)nrows * 4, cudaMemcpyHostToDevice, s));
+            rope_base = m->positions - row0;
         }
     }
     rc = forward_launches(m, kv, ids_dev, S, row0, nrows, rope_base, logits_mode, logits_dev, argmax_dev, 0, s);

@@ -94,8 +94,13 @@ int device_status_word(int **out) {
 
 int device_sm_count() {
     int dev = 0;
-    cudaGetDevice(&dev);
-    return (dev >= 0 && dev < 64 && g_sm_count[dev] > 0) ? g_sm_count[dev] : 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (g_sm_count[dev] <= 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        g_sm_count[dev] = n;
+    }
+    return g_sm_count[dev];
 }
 
 // Tensor-core decode GEMV: W4A16, group 128, bf16 activations.

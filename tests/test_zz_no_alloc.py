@@ -23,20 +23,27 @@ def _cache(p, lens, h=32, kvh=8, hd=128, dtype="int8", seed=40):
     return cache
 
 
-@pytest.mark.parametrize("dtype,act", [("int8", torch.bfloat16), ("f32", torch.float32)])
-def test_static_scratch_entry_point_matches_allocating_one(dtype, act):
+@pytest.mark.parametrize("dtype,act,h,kvh,hd", [("int8", torch.bfloat16, 32, 8, 128), ("f32", torch.float32, 32, 8, 128),
+                                                 ("bf16", torch.bfloat16, 6, 2, 64)])
+def test_static_scratch_entry_point_matches_allocating_one(dtype, act, h, kvh, hd):
     p = pkg()
     lens = [3000, 700]
-    cache = _cache(p, lens, dtype=dtype)
+    cache = _cache(p, lens, h=h, kvh=kvh, hd=hd, dtype=dtype)
     gen = torch.Generator(device="cuda").manual_seed(41)
-    scale = 1 / math.sqrt(128)
-    qs = [torch.randn((2, 32, 128), generator=gen, device="cuda").to(act) for _ in range(2)]
+    scale = 1 / math.sqrt(hd)
+    qs = [torch.randn((2, h, hd), generator=gen, device="cuda").to(act) for _ in range(2)]
     want = [p.dispatch.attention_decode(cache, q, scale) for q in qs]
     outs = [torch.empty_like(q) for q in qs]
+    # the first call on a device looks the array's address up; the calls measured below come after it
+    p.dispatch.attention_decode_static(cache, qs[0], scale, outs[0])
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     # two calls in a row on one stream: the second reuses the scratch the first left behind
     for q, o in zip(qs, outs):
         p.dispatch.attention_decode_static(cache, q, scale, o)
     torch.cuda.synchronize()
+    # the property the entry point exists for: the driver handed out no device memory
+    assert torch.cuda.mem_get_info()[0] >= free_before
     for w, o in zip(want, outs):
         assert torch.isfinite(o.float()).all()
         err = (o.float() - w.float()).abs().max().item() / w.float().abs().max().item()
