@@ -96,17 +96,20 @@ __device__ __forceinline__ void dequant_word(const GemvArgs &a, int n, int word,
     }
 }
 
-// y[m, n] = sum_k x[m, k] * W[n, k] for MT tokens starting at m0.
+// y[m, n] = sum_k x[m, k] * W[n, k] for M tokens, MT at a time: the warp keeps its row and
+// walks the tokens itself (after the first group the row comes from the caches), so a call
+// is one launch whatever M is.
 template <int FMT, typename T, int MT>
-__global__ void __launch_bounds__(256) gemv_generic_kernel(GemvArgs a, const T *x, T *y, int m0,
-                                                           int m_valid) {
+__global__ void __launch_bounds__(256) gemv_generic_kernel(GemvArgs a, const T *x, T *y, int M) {
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int n = blockIdx.x * (blockDim.x >> 5) + warp;
     if (n >= a.N) return;
+    const int words = a.K >> 3;
+  for (int m0 = 0; m0 < M; m0 += MT) {
+    const int m_valid = min(MT, M - m0);
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-    const int words = a.K >> 3;
     for (int word = lane; word < words; word += 32) {
         float w[8];
         dequant_word<FMT>(a, n, word, w);
@@ -127,6 +130,7 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(GemvArgs a, const T *
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         if (lane == 0 && m < m_valid) y[(size_t)(m0 + m) * a.N + n] = from_f32<T>(v);
     }
+  }
 }
 
 }  // namespace ab2

@@ -1,0 +1,184 @@
+// W8A16 decode GEMV: INT8 symmetric weights with one f32 scale per output row
+// (per-output-channel absmax, crates/aarambh-studio-quant/src/qat.rs:140-169; a
+// per-tensor scale, absmax.rs:7-24, is the same with the scale replicated), bf16
+// activations, 1..8 tokens.  HBM-bound: the kernel streams K*N bytes of codes.
+//
+// One CTA owns a 16-row tile of the weight and its 8 warps split K in chunks of
+// 64 columns.  A lane reads 16 bytes of row r and 16 of row r + 8 per chunk
+// (every 32-byte sector fetched is used in full; several chunks are in flight
+// per lane before the first is consumed).  A byte b becomes the f16 value
+// 1152 + b exactly: (b ^ 0x80) is b + 128 as an unsigned byte, and PRMT places it
+// under the exponent of 1024 (0x6400 | u) - one XOR per four weights and one PRMT
+// per pair, no arithmetic.  The pairs feed mma.sync.m16n8k16 (f16 x f16 -> f32)
+// with the 16 rows as A and up to 8 tokens as the columns of B; the 1152 leaves
+// at the end through T = sum of the token's activations:
+//     y[t][n] = scale[n] * (D[n][t] - 1152 T[t]) / 2^e[t].
+// Activations are staged once per CTA as f16 scaled by a power of two per token
+// (exact for bf16 inputs whose magnitudes lie within 2^25 of the token's largest).
+#include <algorithm>
+
+#include "common.cuh"
+#include "gemv_w4a16_m1.cuh"
+
+using namespace ab2;
+
+namespace ab2 {
+namespace {
+
+constexpr int I8S_WARPS = 8;
+constexpr int I8S_UNROLL = 4;   // chunks in flight per warp
+
+template <typename T>
+__device__ __forceinline__ void store_out(T *y, size_t i, float v) { y[i] = from_f32<T>(v); }
+
+__global__ void __launch_bounds__(256)
+gemv_i8_stream_kernel(const int8_t *__restrict__ codes, const float *__restrict__ scales,
+                      const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, int N, int K, int M) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *xs = reinterpret_cast<__half *>(smem_raw);                 // [M][K] f16, scaled
+    __shared__ float tok_T[8], tok_unscale[8];
+    __shared__ float warp_red[I8S_WARPS][8][2];
+    __shared__ float red[I8S_WARPS][16][8];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = lane >> 2, c = lane & 3;
+    const int tile = blockIdx.x;
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // ---- activations: per token, the largest magnitude picks the power of two ----
+    const int nvec = K >> 3;
+    for (int t = 0; t < M; ++t) {
+        const uint4 *x4 = reinterpret_cast<const uint4 *>(x + (size_t)t * K);
+        float amax = 0.f;
+        for (int i = tid; i < nvec; i += 256) {
+            const uint4 v = x4[i];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j] & 0xffff0000u))));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0) warp_red[warp][t][0] = amax;
+    }
+    __syncthreads();
+    for (int t = 0; t < M; ++t) {
+        float amax = 0.f;
+#pragma unroll
+        for (int w = 0; w < I8S_WARPS; ++w) amax = fmaxf(amax, warp_red[w][t][0]);
+        int e = 141 - (int)((__float_as_uint(amax) >> 23) & 0xffu);  // largest magnitude into [2^14, 2^15)
+        e = max(-100, min(100, e));
+        const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
+        const uint4 *x4 = reinterpret_cast<const uint4 *>(x + (size_t)t * K);
+        float sum = 0.f;
+        for (int i = tid; i < nvec; i += 256) {
+            const uint4 v = x4[i];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 hh = __floats2half2_rn(__uint_as_float(w[j] << 16) * sc, __uint_as_float(w[j] & 0xffff0000u) * sc);
+                h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+                const float2 back = __half22float2(hh);
+                sum += back.x + back.y;
+            }
+            *reinterpret_cast<uint4 *>(xs + (size_t)t * K + (size_t)i * 8) = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) warp_red[warp][t][1] = sum;
+        if (tid == 0) tok_unscale[t] = __uint_as_float((uint32_t)(127 - e) << 23);
+    }
+    __syncthreads();
+    if (tid < M) {
+        float T = 0.f;
+#pragma unroll
+        for (int w = 0; w < I8S_WARPS; ++w) T += warp_red[w][tid][1];
+        tok_T[tid] = T;
+    }
+
+    // ---- main loop: this warp's chunks of 64 columns ------------------------------
+    const int row_a = min(tile * 16 + r, N - 1), row_b = min(tile * 16 + r + 8, N - 1);
+    const int8_t *pa = codes + (size_t)row_a * K + c * 16;
+    const int8_t *pb = codes + (size_t)row_b * K + c * 16;
+    const int nchunks = K >> 6;
+    const uint32_t xs_lane = smem_addr(xs) + (uint32_t)(r * K + c * 16) * 2;  // token r, this lane's 16 columns
+    const uint32_t has_x = r < M ? 1u : 0u;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    uint4 xw0 = make_uint4(0u, 0u, 0u, 0u), xw1 = make_uint4(0u, 0u, 0u, 0u);
+    for (int ch0 = warp; ch0 < nchunks; ch0 += I8S_WARPS * I8S_UNROLL) {
+        uint4 wa[I8S_UNROLL], wb[I8S_UNROLL];
+#pragma unroll
+        for (int u = 0; u < I8S_UNROLL; ++u) {
+            const int ch = ch0 + u * I8S_WARPS;
+            if (ch < nchunks) {
+                wa[u] = __ldcs(reinterpret_cast<const uint4 *>(pa + (size_t)ch * 64));
+                wb[u] = __ldcs(reinterpret_cast<const uint4 *>(pb + (size_t)ch * 64));
+            } else {
+                wa[u] = wb[u] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // -128 + 128: see below
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < I8S_UNROLL; ++u) {
+            const int ch = ch0 + u * I8S_WARPS;
+            if (ch >= nchunks) break;
+            lds128_if(has_x, xs_lane + ch * 128, xw0);
+            lds128_if(has_x, xs_lane + ch * 128 + 16, xw1);
+            const uint32_t ua[4] = {wa[u].x ^ 0x80808080u, wa[u].y ^ 0x80808080u, wa[u].z ^ 0x80808080u, wa[u].w ^ 0x80808080u};
+            const uint32_t ub[4] = {wb[u].x ^ 0x80808080u, wb[u].y ^ 0x80808080u, wb[u].z ^ 0x80808080u, wb[u].w ^ 0x80808080u};
+            const uint32_t xb[8] = {xw0.x, xw0.y, xw0.z, xw0.w, xw1.x, xw1.y, xw1.z, xw1.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // word j = columns 4j .. 4j+3 of this lane's 16: pairs (0,1) and (2,3)
+                const uint32_t a0 = __byte_perm(ua[j], 0x64646464u, 0x4140), a2 = __byte_perm(ua[j], 0x64646464u, 0x4342);
+                const uint32_t a1 = __byte_perm(ub[j], 0x64646464u, 0x4140), a3 = __byte_perm(ub[j], 0x64646464u, 0x4342);
+                mma_f16_16816(d, a0, a1, a2, a3, xb[2 * j], xb[2 * j + 1]);
+            }
+        }
+    }
+    // d[0], d[1]: row r, tokens 2c, 2c+1; d[2], d[3]: row r + 8
+    red[warp][r][2 * c] = d[0];
+    red[warp][r][2 * c + 1] = d[1];
+    red[warp][r + 8][2 * c] = d[2];
+    red[warp][r + 8][2 * c + 1] = d[3];
+    __syncthreads();
+    if (tid < 128) {
+        const int row = tid >> 3, tok = tid & 7;
+        const int n = tile * 16 + row;
+        if (tok < M && n < N) {
+            float D = 0.f;
+#pragma unroll
+            for (int w = 0; w < I8S_WARPS; ++w) D += red[w][row][tok];
+            const float v = scales[n] * ((D - 1152.f * tok_T[tok]) * tok_unscale[tok]);
+            y[(size_t)tok * N + n] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+}  // namespace
+
+bool qlinear_i8_stream_eligible(const ab2_qweight *w, ab2_dtype dtype, int M) {
+    return w->fmt == FMT_I8 && dtype == AB2_BF16 && M >= 1 && M <= 8 && w->K % 64 == 0 &&
+           (size_t)M * w->K * 2 <= 96 * 1024;
+}
+
+int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
+    const size_t smem = (size_t)M * w->K * 2;
+    static bool configured[64] = {false};
+    int dev = 0;
+    AB2_CUDA(cudaGetDevice(&dev));
+    AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
+    if (!configured[dev]) {
+        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        configured[dev] = true;
+    }
+    const int tiles = (w->N + 15) / 16;
+    cudaError_t e = launch_kernel(gemv_i8_stream_kernel, dim3(tiles), dim3(256), smem, s, (const int8_t *)w->codes,
+                                  (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "INT8 GEMV launch failed: %s", cudaGetErrorString(e));
+    return AB2_OK;
+}
+
+}  // namespace ab2

@@ -15,6 +15,7 @@
 #include "kv_cache.cuh"
 #include "ops.cuh"
 #include "tp.cuh"
+#include "decode_step_persistent.cuh"
 
 using namespace ab2;
 
@@ -62,6 +63,9 @@ struct ab2_model {
     int *positions;        // [max rows] explicit RoPE offsets
     int *positions_host;   // pinned
     std::map<std::tuple<const void *, const void *, int, int, const void *, const void *, int>, StepGraph> graphs;
+    // one sequence, one token: the whole step as one persistent kernel (null when not eligible)
+    ab2::PersistentStep *persistent;
+    std::vector<ab2::PsLayerDesc> ps_layers;
 };
 
 namespace ab2 {
@@ -347,6 +351,7 @@ AB2_API int ab2_model_create(ab2_model **out, const ab2_model_config *cfg, ab2_d
     m->x = m->xn = m->qkv = m->attn = m->proj = m->gu = m->hid = nullptr;
     m->positions = nullptr; m->positions_host = nullptr;
     m->tp = nullptr; m->lg_local = m->lg_all = nullptr; m->proj32 = nullptr; m->fused_epilogues = false;
+    m->persistent = nullptr;
     *out = m;
     return AB2_OK;
 }
@@ -354,6 +359,7 @@ AB2_API int ab2_model_create(ab2_model **out, const ab2_model_config *cfg, ab2_d
 AB2_API int ab2_model_destroy(ab2_model *m) {
     if (!m) return AB2_OK;
     for (auto &g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    persistent_step_destroy(m->persistent);
     for (auto &L : m->layers) {
         ab2_qweight_destroy(L.wqkv); ab2_qweight_destroy(L.wgu);
         cudaFree(L.norm1); cudaFree(L.norm2);
@@ -477,6 +483,24 @@ AB2_API int ab2_model_finalize(ab2_model *m) {
     int *status_word = nullptr;  // allocate the device status word outside any capture
     int rc = device_status_word(&status_word);
     if (rc != AB2_OK) return rc;
+    persistent_step_destroy(m->persistent);
+    m->persistent = nullptr;
+    if (m->fused_epilogues && !(m->tp && m->tp->world > 1)) {
+        m->ps_layers.resize(c.n_layers);
+        for (int l = 0; l < c.n_layers; ++l) {
+            const LayerWeights &L = m->layers[l];
+            m->ps_layers[l] = PsLayerDesc{L.wqkv, L.part[3], L.wgu, L.part[6], L.norm1, L.norm2};
+        }
+        PsModelDesc d;
+        d.n_layers = c.n_layers; d.d_model = c.d_model; d.n_heads = c.n_heads; d.n_kv_heads = c.n_kv_heads;
+        d.head_dim = c.head_dim; d.ffn_hidden = c.ffn_hidden; d.vocab = c.vocab; d.eps = c.rms_eps;
+        d.embedding = m->embedding; d.lm_head = m->lm_head; d.final_norm = m->final_norm;
+        d.layers = m->ps_layers.data();
+        d.x = m->x; d.qkv = m->qkv; d.attn = m->attn; d.hid = m->hid;
+        d.cos_t = m->cos_t; d.sin_t = m->sin_t;
+        rc = persistent_step_create(&m->persistent, d);
+        if (rc != AB2_OK) return rc;
+    }
     m->finalized = true;
     return AB2_OK;
 }
@@ -521,6 +545,12 @@ AB2_API int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev,
     return kv_commit_device(kv, S, row0, nrows, s);
 }
 
+AB2_API int ab2_model_step_trace(const ab2_model *m, unsigned long long *values_host, int capacity, int *nphases) {
+    AB2_REQUIRE(m && values_host && nphases, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(m->persistent != nullptr, AB2_ERR_UNSUPPORTED, "this model does not run its decode step as one persistent kernel");
+    return persistent_step_trace(m->persistent, values_host, capacity, nphases);
+}
+
 AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int row0, int nrows,
                                   void *logits_dev, uint32_t *argmax_dev, ab2_stream stream) {
     int rc = check_forward(m, kv, ids_dev, 1, row0, nrows, nullptr, logits_dev ? 1 : 0, logits_dev);
@@ -537,6 +567,18 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
     // launch cannot read: graphs are kept per power-of-two bound of the longest row.
     int longest = 1;
     for (int r = row0; r < row0 + nrows; ++r) longest = std::max(longest, kv->lens_host[r] + 1);
+    if (nrows == 1 && m->persistent && persistent_step_serves(m->persistent, kv, longest)) {
+        // one sequence: the whole step is one persistent kernel (no graph needed)
+        void *lg = logits_dev ? logits_dev : m->gu;
+        rc = persistent_step_launch(m->persistent, kv, ids_dev, row0, lg, argmax_dev, s);
+        if (rc == AB2_OK) {
+            kv->lens_host[row0] += 1;
+            return AB2_OK;
+        }
+        // the launch was refused (for instance, not every CTA can be resident): use the graph path from now on
+        persistent_step_destroy(m->persistent);
+        m->persistent = nullptr;
+    }
     int len_bound = 512;
     while (len_bound < longest) len_bound <<= 1;
     len_bound = std::min(len_bound, kv->cap);

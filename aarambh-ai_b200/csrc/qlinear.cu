@@ -27,12 +27,10 @@ template <int FMT, typename T>
 static int launch_generic(const ab2_qweight *w, const T *x, int M, T *y, cudaStream_t s) {
     GemvArgs a = gemv_args_of(w);
     dim3 grid((w->N + 7) / 8), block(256);
-    for (int m0 = 0; m0 < M; m0 += 4) {
-        int mv = M - m0 < 4 ? M - m0 : 4;
-        if (mv == 1) gemv_generic_kernel<FMT, T, 1><<<grid, block, 0, s>>>(a, x, y, m0, 1);
-        else if (mv == 2) gemv_generic_kernel<FMT, T, 2><<<grid, block, 0, s>>>(a, x, y, m0, 2);
-        else gemv_generic_kernel<FMT, T, 4><<<grid, block, 0, s>>>(a, x, y, m0, mv);
-    }
+    // one launch whatever the token count: the kernel walks the tokens in groups of MT
+    if (M == 1) gemv_generic_kernel<FMT, T, 1><<<grid, block, 0, s>>>(a, x, y, M);
+    else if (M == 2) gemv_generic_kernel<FMT, T, 2><<<grid, block, 0, s>>>(a, x, y, M);
+    else gemv_generic_kernel<FMT, T, 4><<<grid, block, 0, s>>>(a, x, y, M);
     AB2_LAUNCH_CHECK();
     return AB2_OK;
 }
@@ -91,6 +89,12 @@ int device_status_word(int **out) {
     *out = g_status_word[dev];
     return AB2_OK;
 }
+
+// Counts the times ab2_device_status found a wait that had run out.  Objects that keep
+// counters in device memory compare it with the value they saw last and put their
+// counters back to rest when it moved (a kernel that gave up may have left them part-way).
+static int g_recovery_epoch = 0;
+int device_recovery_epoch() { return g_recovery_epoch; }
 
 int device_sm_count() {
     int dev = 0;
@@ -321,6 +325,8 @@ int qlinear_w4a16_norm_peer(const ab2_qweight *w, const void *x, const float *no
 }
 
 int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
+bool qlinear_i8_stream_eligible(const ab2_qweight *w, ab2_dtype dtype, int M);
+int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {
     if (qlinear_w4a16_mma_eligible(w, dtype)) {
@@ -330,6 +336,8 @@ int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype
         if (M <= 64) return qlinear_w4a16_mma(w, x, M, y, s);
         return qlinear_w4a16_tc(w, x, M, y, s);
     }
+    // INT8 weights, bf16 activations, a few tokens: the HBM-bound streaming GEMV
+    if (qlinear_i8_stream_eligible(w, dtype, M)) return qlinear_i8_stream(w, x, M, y, s);
     return qlinear_generic(w, x, M, dtype, y, s);
 }
 
@@ -350,5 +358,6 @@ AB2_API int ab2_device_status(int *status_host) {
     AB2_CUDA(cudaDeviceSynchronize());
     AB2_CUDA(cudaMemcpy(status_host, word, sizeof(int), cudaMemcpyDeviceToHost));
     AB2_CUDA(cudaMemset(word, 0, sizeof(int)));
+    if (*status_host != 0) ++g_recovery_epoch;
     return AB2_OK;
 }

@@ -123,6 +123,15 @@ class AarambhModel:
                                         logits.data_ptr() if logits is not None else None,
                                         argmax_dev.data_ptr() if argmax_dev is not None else None, stream_ptr()))
 
+    def step_trace(self):
+        """Phase timestamps (ns) of the last persistent one-row decode step as an int64
+        array [3 CTAs, phases, 4]: phase start, prologue done, CTA done, barrier passed."""
+        import numpy as np
+        n = C.c_int(0)
+        buf = np.zeros(3 * 4096 * 4, np.uint64)
+        check(lib.ab2_model_step_trace(self._h, buf.ctypes.data, buf.size, C.byref(n)))
+        return buf[:3 * n.value * 4].astype(np.int64).reshape(3, n.value, 4)
+
     def __del__(self):
         try:
             if self._h:

@@ -334,6 +334,14 @@ int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, 
  * argmax_dev may be passed as the next ids_dev. */
 int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int row0, int nrows,
                           void *logits_dev, uint32_t *argmax_dev, ab2_stream stream);
+/* Profiling aid (no counterpart in the reference): when the last one-row decode step ran as
+ * the single persistent kernel, copies the GPU wall-clock timestamps (ns) of its phases to
+ * values_host as [3 CTAs: first, middle, last][phase][4] = {phase start, prologue done,
+ * CTA done, grid barrier passed}; phases are embedding, then per block {qkv, attention, o,
+ * gate|up, down}, the LM head, and the tail (argmax, length commit).  *nphases receives the
+ * phase count; AB2_ERR_UNSUPPORTED when the model does not use that kernel, AB2_ERR_CAPACITY
+ * when `capacity` (in values) is less than 12 * phases.  Synchronises the device. */
+int ab2_model_step_trace(const ab2_model *m, unsigned long long *values_host, int capacity, int *nphases);
 
 #ifdef __cplusplus
 }
