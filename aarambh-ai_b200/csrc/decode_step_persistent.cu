@@ -50,7 +50,7 @@ constexpr int PS_THREADS = PS_WARPS * 32;
 constexpr int PS_STAGES = 6;
 constexpr int PS_NV = 3;           // vectors of 8 activations a thread holds between the prologue passes
 constexpr int PS_MAX_K = 16384;    // <= PS_THREADS * 8 * PS_NV
-constexpr int PS_LOCAL_TILES = 64;
+constexpr int PS_LOCAL_TILES = 128;  // tiles of one projection a CTA may own
 constexpr int PS_HD = 128;
 constexpr int PS_MAX_CTA_TOKENS = 520;  // cached tokens one CTA attends (context bound / splits + the new one)
 constexpr uint32_t PS_BLOCK_BYTES = W4_BLOCK_WORDS * 4;
@@ -84,8 +84,6 @@ struct PsArgs {
     float *apart_acc;      // [kvh][nsplit][rep][128]
     float *apart_ml;       // [kvh][nsplit][rep][2]
     int *acount;           // [kvh], zero at rest
-    float *partials;       // cut tiles of the projections: [warps of the grid][2][W4W_SLOT_FLOATS]
-    int *counters;         // [tiles], zero at rest
     unsigned int *bar;     // grid barrier: arrivals since the scratch was made
     unsigned int bar_base; // arrivals before this launch
     int *status;
@@ -137,9 +135,10 @@ __host__ __device__ constexpr size_t ps_act_bytes() {
     size_t gemv = (size_t)PS_MAX_K * 2 + (size_t)(PS_MAX_K >> 7) * 8;
     return gemv > sizeof(PsAttnSmem) ? gemv : sizeof(PsAttnSmem);
 }
-__host__ __device__ constexpr size_t ps_smem_bytes() {
+// rings, activation / attention area, mbarriers, then a copy of the op list
+__host__ __device__ constexpr size_t ps_smem_bytes(int nops) {
     return (size_t)PS_WARPS * PS_STAGES * PS_BLOCK_BYTES + ((ps_act_bytes() + 127) / 128) * 128 +
-           (size_t)PS_WARPS * PS_STAGES * 8;
+           (size_t)PS_WARPS * PS_STAGES * 8 + (size_t)nops * sizeof(PsOp);
 }
 
 __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(const PsArgs a) {
@@ -152,7 +151,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;
-    const int nwarps = (int)gridDim.x * PS_WARPS, wid = (int)blockIdx.x * PS_WARPS + warp;
 
     const uint32_t smem0 = smem_addr(smem_raw);
     const uint32_t act0 = smem0 + PS_WARPS * PS_STAGES * PS_BLOCK_BYTES;  // activations / attention area
@@ -162,6 +160,24 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
     const uint32_t ring_end = ring0 + PS_STAGES * PS_BLOCK_BYTES;
     const uint32_t lane0 = lane == 0 ? 1u : 0u;
 
+    // the op list lives in shared memory: a phase must not start with a round trip for its descriptor
+    const PsOp *ops = reinterpret_cast<const PsOp *>(smem_raw + (size_t)PS_WARPS * PS_STAGES * PS_BLOCK_BYTES +
+                                                      ((ps_act_bytes() + 127) / 128) * 128 + (size_t)PS_WARPS * PS_STAGES * 8);
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.ops);
+        uint4 *dst = reinterpret_cast<uint4 *>(const_cast<PsOp *>(ops));
+        for (int i = tid; i < a.nops * (int)(sizeof(PsOp) / 16); i += PS_THREADS) dst[i] = src[i];
+    }
+    // A projection's 16-row tiles are dealt to the CTAs in contiguous runs (equal to within one
+    // tile) and the blocks of a CTA's tiles to its warps in contiguous runs (equal to within one
+    // block): a tile is finished inside one CTA, through shared memory.
+    auto cta_tiles = [&](int N, int &tile_lo, int &ntile) {
+        const int tiles = (N + 15) >> 4;
+        const int tb = tiles / (int)gridDim.x, tr = tiles - tb * (int)gridDim.x;
+        tile_lo = (int)blockIdx.x * tb + min((int)blockIdx.x, tr);
+        ntile = tb + ((int)blockIdx.x < tr ? 1 : 0);
+    };
+
     if (tid == 0) s_abort = 0;
     if (lane == 0) {
 #pragma unroll
@@ -170,7 +186,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    __syncwarp();
+    __syncthreads();
 
     // ---- the fetch cursor: walks this warp's block ranges of every projection, in order
     int f_op = -1, f_left = 0;
@@ -180,11 +196,13 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
         while (f_left == 0 && f_op < a.nops) {
             ++f_op;
             if (f_op >= a.nops) break;
-            if (a.ops[f_op].kind != PS_GEMV) continue;
-            const int total = ((a.ops[f_op].N + 15) >> 4) * (a.ops[f_op].K >> 7);
-            const int base = total / nwarps, rem = total - base * nwarps;
-            f_left = base + (wid < rem ? 1 : 0);
-            f_src = a.ops[f_op].wt + (size_t)(wid * base + min(wid, rem)) * W4_BLOCK_WORDS;
+            if (ops[f_op].kind != PS_GEMV) continue;
+            int tile_lo, ntile;
+            cta_tiles(ops[f_op].N, tile_lo, ntile);
+            const int G = ops[f_op].K >> 7, nb = ntile * G;
+            const int base = nb / PS_WARPS, rem = nb - base * PS_WARPS;
+            f_left = base + (warp < rem ? 1 : 0);
+            f_src = ops[f_op].wt + ((size_t)tile_lo * G + warp * base + min(warp, rem)) * W4_BLOCK_WORDS;
         }
     };
     auto refill = [&](uint32_t stage, uint32_t bar) {
@@ -200,6 +218,15 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
 #pragma unroll
     for (int j = 0; j < PS_STAGES; ++j) refill(ring0 + j * PS_BLOCK_BYTES, bar0 + j * 8);
 
+    // ---- attention geometry: the same in every block (one sequence, one new token)
+    const int att_on = (int)blockIdx.x < a.kv.kvh * a.nsplit ? 1 : 0;
+    const int att_kvhead = (int)blockIdx.x / a.nsplit, att_rank = (int)blockIdx.x % a.nsplit;
+    const int att_pos = a.kv.lens[a.row];
+    const int att_chunk = (att_pos + a.nsplit - 1) / a.nsplit;
+    const int att_c0 = min(att_pos, att_rank * att_chunk);
+    const int att_ncached = att_on ? min(att_pos, att_c0 + att_chunk) - att_c0 : 0;
+    const size_t att_head_base = ((size_t)a.row * a.kv.kvh + (att_on ? att_kvhead : 0)) * a.kv.cap;
+
     uint32_t cur = ring0, bar = bar0, parity = 0;
     bool dead = false;  // a copy of this warp never arrived: it only keeps the barriers company
     uint32_t k_lo = 0x000F000Fu, k_hi = 0x00F000F0u, k_magic = 0x64006400u;
@@ -212,7 +239,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
     };
 
     for (int oi = 0; oi < a.nops; ++oi) {
-        const PsOp &op = a.ops[oi];
+        const PsOp &op = ops[oi];
         const int kind = op.kind;
         stamp(oi, 0);
         if (kind != PS_GEMV) stamp(oi, 1);
@@ -231,15 +258,18 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                 a.x[k] = __float2bfloat16_rn(v);
             }
         } else if (kind == PS_GEMV) {
-            const int K = op.K, N = op.N, G = K >> 7, tiles = (N + 15) >> 4;
-            const int total = tiles * G;
-            const int base = total / nwarps, rem = total - base * nwarps;
-            const int b0 = wid * base + min(wid, rem);
-            const int nblk = base + (wid < rem ? 1 : 0);
+            const int K = op.K, N = op.N, G = K >> 7;
+            int tile_lo, ntile;
+            cta_tiles(N, tile_lo, ntile);
+            const int nb = ntile * G;  // blocks of this CTA, numbered from its first tile
+            const int base = nb / PS_WARPS, rem = nb - base * PS_WARPS;
+            const int b0 = warp * base + min(warp, rem);
+            const int nblk = base + (warp < rem ? 1 : 0);
             const int b1 = b0 + nblk;
             const uint32_t xs0 = act0, gs0 = act0 + K * 2;
             const float *norm_w = op.norm_w;
             if (tid < PS_LOCAL_TILES) cta_cnt[tid] = 0;
+          if (ntile > 0) {  // a CTA without tiles of this projection has nothing to prepare
 
             // ---- prologue, pass 1: sum of squares and largest magnitude ----------
             const uint4 *x4 = reinterpret_cast<const uint4 *>(op.x);
@@ -348,12 +378,10 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
             const uint32_t param_off = (256 + r) * 4;
             const uint32_t has_x = r == 0 ? 1u : 0u;
             const uint32_t xlane = xs0 + c * 64;
-            const int cta_w0 = (int)blockIdx.x * PS_WARPS;
-            const int cta_tile0 = (cta_w0 * base + min(cta_w0, rem)) / G;
             __nv_bfloat16 *y = op.y ? op.y : a.logits;
             const int epi = op.epi;
 
-            int tile = b0 / G, g = b0 - tile * G;
+            int lt = b0 / G, g = b0 - lt * G;  // tile of the CTA, group
             uint4 xw[4];
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) xw[wi] = make_uint4(0u, 0u, 0u, 0u);
@@ -419,54 +447,32 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                 float va = acc_a * unscale, vb = acc_b * unscale;
                 bool store = whole;
                 if (!whole) {
+                    // contributors: the warps of this CTA whose ranges meet [lt*G, lt*G + G)
                     const int cut = rem * (base + 1);
-                    const int first_b = tile * G, last_b = first_b + G - 1;
+                    const int first_b = lt * G, last_b = first_b + G - 1;
                     const int w_first = first_b < cut ? first_b / (base + 1) : rem + (first_b - cut) / base;
                     const int w_last = last_b < cut ? last_b / (base + 1) : rem + (last_b - cut) / base;
-                    const int which = wid == w_first ? 1 : 0;
-                    const int li = tile - cta_tile0;
-                    float sum_a = 0.f, sum_b = 0.f;
-                    bool last = false;
-                    if (w_first / PS_WARPS == (int)blockIdx.x && w_last / PS_WARPS == (int)blockIdx.x && li < PS_LOCAL_TILES) {
-                        if (c == 0) cta_part[warp][which][r] = make_float2(va, vb);
+                    const int which = warp == w_first ? 1 : 0;  // slot 1: the tile my range ends inside
+                    if (c == 0) cta_part[warp][which][r] = make_float2(va, vb);
+                    __threadfence_block();
+                    __syncwarp();
+                    int arrived = 0;
+                    if (lane == 0) arrived = atomicAdd(&cta_cnt[lt], 1);
+                    arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                    store = arrived == w_last - w_first;
+                    if (store) {
                         __threadfence_block();
-                        __syncwarp();
-                        int arrived = 0;
-                        if (lane == 0) arrived = atomicAdd(&cta_cnt[li], 1);
-                        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                        last = arrived == w_last - w_first;
-                        if (last) {
-                            __threadfence_block();
-                            for (int w = w_first; w <= w_last; ++w) {
-                                const float2 v = cta_part[w % PS_WARPS][w == w_first ? 1 : 0][r];
-                                sum_a += v.x;
-                                sum_b += v.y;
-                            }
+                        float sum_a = 0.f, sum_b = 0.f;
+                        for (int w = w_first; w <= w_last; ++w) {  // contributor order: the sum does not depend on arrival order
+                            const float2 v = cta_part[w][w == w_first ? 1 : 0][r];
+                            sum_a += v.x;
+                            sum_b += v.y;
                         }
-                    } else {
-                        float *mine = a.partials + ((size_t)wid * 2 + which) * W4W_SLOT_FLOATS + r * 2;
-                        if (c == 0) *reinterpret_cast<float2 *>(mine) = make_float2(va, vb);
-                        __threadfence();
-                        __syncwarp();
-                        int arrived = 0;
-                        if (lane == 0) arrived = atomicAdd(&a.counters[tile], 1);
-                        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                        last = arrived == w_last - w_first;
-                        if (last) {
-                            __threadfence();
-                            for (int w = w_first; w <= w_last; ++w) {
-                                const float *p = a.partials + ((size_t)w * 2 + (w == w_first ? 1 : 0)) * W4W_SLOT_FLOATS + r * 2;
-                                const float2 v = __ldcg(reinterpret_cast<const float2 *>(p));
-                                sum_a += v.x;
-                                sum_b += v.y;
-                            }
-                            if (lane == 0) a.counters[tile] = 0;
-                        }
+                        va = sum_a;
+                        vb = sum_b;
                     }
-                    store = last;
-                    va = sum_a;
-                    vb = sum_b;
                 }
+                const int tile = tile_lo + lt;
                 if (store && c == 0) {
                     if (epi == W4_EPI_SWIGLU) {
                         const int col = tile * 8 + r;
@@ -484,26 +490,24 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                     }
                 }
                 g = 0;
-                ++tile;
+                ++lt;
             }
+          }  // ntile > 0
         } else if (kind == PS_ATTN) {
             const int nsplit = a.nsplit, rep = a.rep, kvh = a.kv.kvh;
-            if ((int)blockIdx.x < kvh * nsplit && !(a.debug & 2)) {
+            if (att_on && !(a.debug & 2)) {
                 PsAttnSmem &S = *reinterpret_cast<PsAttnSmem *>(act_ptr);
-                const int kvhead = (int)blockIdx.x / nsplit, rank = (int)blockIdx.x % nsplit;
-                const int row = a.row;
+                const int kvhead = att_kvhead, rank = att_rank;
                 constexpr int half = PS_HD / 2;
-                const int pos = a.kv.lens[row];
+                const int pos = att_pos;
                 const size_t layer_off = (size_t)op.layer * a.kv_layer_tokens;
                 const int8_t *kc = (const int8_t *)a.kv.k + layer_off * PS_HD;
                 const int8_t *vc = (const int8_t *)a.kv.v + layer_off * PS_HD;
                 float *ksc = a.kv.ks + layer_off, *vsc = a.kv.vs + layer_off;
-                const size_t head_base = ((size_t)row * kvh + kvhead) * a.kv.cap;
+                const size_t head_base = att_head_base;
                 const float *cs = a.cos_t + (size_t)pos * half, *sn = a.sin_t + (size_t)pos * half;
                 // cached tokens of this CTA; the last split also owns the new token
-                const int chunk = (pos + nsplit - 1) / nsplit;
-                const int c0 = min(pos, rank * chunk), c1 = min(pos, c0 + chunk);
-                const int ncached = c1 - c0;
+                const int c0 = att_c0, ncached = att_ncached;
                 const bool owns_new = rank == nsplit - 1;
                 const int ntok = ncached + (owns_new ? 1 : 0);
 
@@ -690,16 +694,25 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                     __threadfence();
                     for (int i = tid; i < rep * PS_HD; i += PS_THREADS) {
                         const int hh = i / PS_HD, d = i % PS_HD;
+                        // every load of the thread is in flight before the first is used (at most 16 splits)
+                        float mv[16], lv[16], av[16];
+#pragma unroll
+                        for (int s2 = 0; s2 < 16; ++s2) {
+                            const size_t pb = ((size_t)kvhead * nsplit + min(s2, nsplit - 1)) * rep + hh;
+                            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(&a.apart_ml[pb * 2]));
+                            mv[s2] = s2 < nsplit ? ml.x : -INFINITY;
+                            lv[s2] = ml.y;
+                            av[s2] = __ldcg(&a.apart_acc[pb * PS_HD + d]);
+                        }
                         float M = -INFINITY;
-                        for (int s2 = 0; s2 < nsplit; ++s2)
-                            M = fmaxf(M, __ldcg(&a.apart_ml[(((size_t)kvhead * nsplit + s2) * rep + hh) * 2]));
+#pragma unroll
+                        for (int s2 = 0; s2 < 16; ++s2) M = fmaxf(M, mv[s2]);
                         float L = 0.f, A = 0.f;
-                        for (int s2 = 0; s2 < nsplit; ++s2) {
-                            const size_t pb = ((size_t)kvhead * nsplit + s2) * rep + hh;
-                            const float mv = __ldcg(&a.apart_ml[pb * 2]);
-                            const float e2 = (mv == -INFINITY) ? 0.f : expf(mv - M);
-                            L += e2 * __ldcg(&a.apart_ml[pb * 2 + 1]);
-                            A += e2 * __ldcg(&a.apart_acc[pb * PS_HD + d]);
+#pragma unroll
+                        for (int s2 = 0; s2 < 16; ++s2) {
+                            const float e2 = (mv[s2] == -INFINITY) ? 0.f : expf(mv[s2] - M);
+                            L += e2 * lv[s2];
+                            A += e2 * av[s2];
                         }
                         a.attn[(size_t)(kvhead * rep + hh) * PS_HD + d] = __float2bfloat16_rn(L > 0.f ? A * (1.0f / L) : A);
                     }
@@ -740,11 +753,30 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
         // ---- grid barrier: the next phase reads what this one wrote ------------------
         if (oi + 1 < a.nops) {
             ++barrier_no;
+            // what the next phase reads and this launch never writes is pulled into L1 while the
+            // CTA waits: the RMSNorm weight, or the cached K / V rows of this CTA's tokens
+            {
+                const PsOp &nx = ops[oi + 1];
+                if (nx.kind == PS_GEMV && nx.norm_w) {
+                    for (int i = tid; i < nx.K >> 5; i += PS_THREADS)
+                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(nx.norm_w + (size_t)i * 32));
+                } else if (nx.kind == PS_ATTN && att_ncached > 0) {
+                    const size_t layer_off = (size_t)nx.layer * a.kv_layer_tokens;
+                    const size_t trow0 = layer_off + att_head_base + att_c0;
+                    if (tid < att_ncached) {
+                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"((const int8_t *)a.kv.k + (trow0 + tid) * PS_HD));
+                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"((const int8_t *)a.kv.v + (trow0 + tid) * PS_HD));
+                    }
+                    if (tid * 32 < att_ncached) {  // scale words: 32 per line
+                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(a.kv.ks + trow0 + tid * 32));
+                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(a.kv.vs + trow0 + tid * 32));
+                    }
+                }
+            }
             __syncthreads();
             stamp(oi, 2);
             if (tid == 0) {
                 const unsigned int target = a.bar_base + barrier_no * gridDim.x;
-                __threadfence();
                 asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(a.bar) : "memory");
                 bool ok = false;
                 unsigned long long t_start = 0;
@@ -786,8 +818,8 @@ struct PersistentStep {
     PsOp *ops_dev = nullptr;
     int nops = 0, grid = 0, nsplit = 1, device = 0;
     PsModelDesc desc;
-    float *apart_acc = nullptr, *apart_ml = nullptr, *partials = nullptr;
-    int *acount = nullptr, *counters = nullptr;
+    float *apart_acc = nullptr, *apart_ml = nullptr;
+    int *acount = nullptr;
     unsigned int *bar = nullptr;
     unsigned int bar_total = 0;  // arrivals the barrier word has seen once every launch so far has finished
     int max_tiles = 0, recovery_epoch = 0;
@@ -814,7 +846,9 @@ int persistent_step_create(PersistentStep **out, const PsModelDesc &d) {
     AB2_CUDA(cudaGetDevice(&dev));
     AB2_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
     if (!coop) return AB2_OK;
-    const size_t smem = ps_smem_bytes();
+    const int nops_of_model = 1 + 5 * d.n_layers + 2;
+    const size_t smem = ps_smem_bytes(nops_of_model);
+    if (smem > 220 * 1024) return AB2_OK;  // too many blocks for the shared copy of the op list
     if (cudaFuncSetAttribute(decode_step_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return AB2_OK;
@@ -857,18 +891,18 @@ int persistent_step_create(PersistentStep **out, const PsModelDesc &d) {
     t.kind = PS_TAIL;
     ops.push_back(t);
     ps->nops = (int)ops.size();
+    if ((ps->max_tiles + grid - 1) / grid > PS_LOCAL_TILES) {  // a CTA finishes its tiles through a fixed table
+        delete ps;
+        return AB2_OK;
+    }
 
     const size_t parts = (size_t)d.n_kv_heads * ps->nsplit * rep;
-    const size_t nwarps = (size_t)grid * PS_WARPS;
     cudaError_t err = cudaMalloc((void **)&ps->ops_dev, ops.size() * sizeof(PsOp));
     if (err == cudaSuccess) err = cudaMemcpy(ps->ops_dev, ops.data(), ops.size() * sizeof(PsOp), cudaMemcpyHostToDevice);
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->apart_acc, parts * PS_HD * sizeof(float));
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->apart_ml, parts * 2 * sizeof(float));
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->acount, (size_t)d.n_kv_heads * sizeof(int));
     if (err == cudaSuccess) err = cudaMemset(ps->acount, 0, (size_t)d.n_kv_heads * sizeof(int));
-    if (err == cudaSuccess) err = cudaMalloc((void **)&ps->partials, nwarps * 2 * W4W_SLOT_FLOATS * sizeof(float));
-    if (err == cudaSuccess) err = cudaMalloc((void **)&ps->counters, (size_t)ps->max_tiles * sizeof(int));
-    if (err == cudaSuccess) err = cudaMemset(ps->counters, 0, (size_t)ps->max_tiles * sizeof(int));
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->trace, (size_t)3 * ops.size() * 4 * sizeof(unsigned long long));
     if (err == cudaSuccess) err = cudaMemset(ps->trace, 0, (size_t)3 * ops.size() * 4 * sizeof(unsigned long long));
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->bar, sizeof(unsigned int));
@@ -886,7 +920,7 @@ int persistent_step_create(PersistentStep **out, const PsModelDesc &d) {
 void persistent_step_destroy(PersistentStep *ps) {
     if (!ps) return;
     cudaFree(ps->ops_dev); cudaFree(ps->apart_acc); cudaFree(ps->apart_ml); cudaFree(ps->acount);
-    cudaFree(ps->partials); cudaFree(ps->counters); cudaFree(ps->bar); cudaFree(ps->trace);
+    cudaFree(ps->bar); cudaFree(ps->trace);
     delete ps;
 }
 
@@ -916,7 +950,6 @@ int persistent_step_launch(PersistentStep *ps, ab2_kv *kv, const uint32_t *ids_d
         // a wait ran out in some earlier kernel on this device: counters may hold partial
         // counts; put them back to rest before the next step relies on them
         AB2_CUDA(cudaStreamSynchronize(s));
-        AB2_CUDA(cudaMemset(ps->counters, 0, (size_t)ps->max_tiles * sizeof(int)));
         AB2_CUDA(cudaMemset(ps->acount, 0, (size_t)d.n_kv_heads * sizeof(int)));
         AB2_CUDA(cudaMemcpy(ps->bar, &ps->bar_total, sizeof(unsigned int), cudaMemcpyHostToDevice));
         ps->recovery_epoch = device_recovery_epoch();
@@ -932,7 +965,6 @@ int persistent_step_launch(PersistentStep *ps, ab2_kv *kv, const uint32_t *ids_d
     a.kv_layer_tokens = (size_t)kv->B * kv->kvh * kv->cap;
     a.row = row; a.h = d.n_heads; a.rep = d.n_heads / d.n_kv_heads; a.nsplit = ps->nsplit;
     a.apart_acc = ps->apart_acc; a.apart_ml = ps->apart_ml; a.acount = ps->acount;
-    a.partials = ps->partials; a.counters = ps->counters;
     a.bar = ps->bar; a.bar_base = ps->bar_total;
     a.status = status;
     a.logits = (__nv_bfloat16 *)logits_dev; a.vocab = d.vocab; a.argmax_out = argmax_dev;
@@ -942,7 +974,7 @@ int persistent_step_launch(PersistentStep *ps, ab2_kv *kv, const uint32_t *ids_d
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ps->grid); cfg.blockDim = dim3(PS_THREADS);
-    cfg.dynamicSmemBytes = ps_smem_bytes(); cfg.stream = s;
+    cfg.dynamicSmemBytes = ps_smem_bytes(ps->nops); cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;

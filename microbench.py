@@ -4,10 +4,10 @@ benchmark specification's shapes.  Timing is with CUDA events on the launching
 stream after warm-up; weights / caches larger than L2 are cycled so every timed
 launch reads from HBM.
 
-    python aarambh-ai_b200/microbench.py gemv      [--m 1,4,16]      W4A16 dequant-GEMV (HBM GB/s)
-    python aarambh-ai_b200/microbench.py gemm      [--m 512,2048]    W4A16 tcgen05 GEMM (TFLOP/s)
-    python aarambh-ai_b200/microbench.py attention [--cases 8x16384] INT8-KV flash-decode (HBM GB/s)
-    python aarambh-ai_b200/microbench.py step      [--layers 2] [--ctx 512] one-token decoder step of a short
+    python microbench.py gemv      [--m 1,4,16]      W4A16 dequant-GEMV (HBM GB/s)
+    python microbench.py gemm      [--m 512,2048]    W4A16 tcgen05 GEMM (TFLOP/s)
+    python microbench.py attention [--cases 8x16384] INT8-KV flash-decode (HBM GB/s)
+    python microbench.py step      [--layers 2] [--ctx 512] one-token decoder step of a short
                                                    Large-shaped stack (a few hundred MB on the device: the
                                                    case to capture the step's kernels under a profiler)
 
@@ -23,7 +23,7 @@ import sys
 
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 from __graft_entry__ import import_package  # noqa: E402
 
