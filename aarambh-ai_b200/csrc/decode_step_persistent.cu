@@ -23,6 +23,15 @@
 // (max, sum, accumulator) in global memory, and the last CTA of a head to arrive
 // merges the partials (log-sum-exp) and writes the head's output.
 //
+// Status: opt-in (AB2_PERSISTENT_STEP=1).  Measured on the Large-class decoder (one B200, context
+// 512): 1.98 ms per step against 1.82 ms for the graph-replayed chain of kernels.  What a phase
+// costs here besides its weight stream: the grid barrier (1.3 us), the projection prologue on
+// 768 threads (2 to 3.5 us, every CTA converts the whole activation vector), the attention phase
+// (10 us: a chain of dependent L2 round trips through three CTA barriers, the split merge and an
+// atomic), and the one-tile imbalance of dealing 16-row tiles to 148 CTAs.  The weight rings do
+// stream across the barriers as intended (the first blocks of a phase are resident when it
+// starts), but the fixed costs above outweigh the kernel boundaries they replace.
+//
 // Every wait is bounded (two seconds of wall clock): a barrier or copy that never
 // completes records AB2_ERR_TIMEOUT in the status word, the CTA waits (bounded)
 // for its own copies in flight and returns.
@@ -52,6 +61,7 @@ constexpr int PS_NV = 3;           // vectors of 8 activations a thread holds be
 constexpr int PS_MAX_K = 16384;    // <= PS_THREADS * 8 * PS_NV
 constexpr int PS_LOCAL_TILES = 128;  // tiles of one projection a CTA may own
 constexpr int PS_HD = 128;
+constexpr int PS_TRACE = 10;         // timestamps kept per phase and traced CTA
 constexpr int PS_MAX_CTA_TOKENS = 520;  // cached tokens one CTA attends (context bound / splits + the new one)
 constexpr uint32_t PS_BLOCK_BYTES = W4_BLOCK_WORDS * 4;
 
@@ -91,7 +101,6 @@ struct PsArgs {
     int vocab;
     uint32_t *argmax_out;  // or null
     unsigned long long *trace;  // [3 CTAs][nops][4] timestamps (ns): phase start, prologue done, CTA done, barrier passed
-    int debug;                  // measurement only: 1 skips the projections' main loops, 2 the attention body
 };
 
 __device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16 *p) {
@@ -120,6 +129,21 @@ __device__ __forceinline__ long long ps_argmax_key(float v, int idx) {
     return ((long long)b << 32) | (unsigned)idx;
 }
 
+// floor(n / d) for small non-negative n and positive d without the integer-division sequence
+// (this runs once per cut tile, in code that is fetched cold every phase).
+__device__ __forceinline__ int ps_div_floor(int n, int d) {
+    int q = (int)__fdividef((float)n + 0.5f, (float)d);
+    if (q * d > n) --q;
+    else if ((q + 1) * d <= n) ++q;
+    return q;
+}
+// The warp whose contiguous run holds block b when nb = 24 * base + rem blocks are dealt to 24
+// warps, the first `rem` of them taking base + 1.
+__device__ __forceinline__ int ps_warp_of_block(int b, int base, int rem) {
+    const int cut = rem * (base + 1);
+    return b < cut ? ps_div_floor(b, base + 1) : rem + ps_div_floor(b - cut, base);
+}
+
 // Shared memory of the attention phase; it aliases the activation area of the
 // projection phases (a grid barrier lies between any two uses).
 struct PsAttnSmem {
@@ -129,6 +153,7 @@ struct PsAttnSmem {
     float newk[PS_HD], newv[PS_HD];     // the new token as the cache will return it
     float pacc[PS_WARPS][PS_HD];        // P.V per (token subset, head) warp
     float hm[4], hl[4];                 // this CTA's running max and sum per head
+    float mlbuf[4][16][2];              // (max, sum) of every split of the head, for the merge
 };
 
 __host__ __device__ constexpr size_t ps_act_bytes() {
@@ -141,6 +166,142 @@ __host__ __device__ constexpr size_t ps_smem_bytes(int nops) {
            (size_t)PS_WARPS * PS_STAGES * 8 + (size_t)nops * sizeof(PsOp);
 }
 
+
+// Named barrier over `count` threads (a multiple of 32).
+__device__ __forceinline__ void ps_bar(int id, int count) {
+    asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+}
+
+// The projection prologue of one CTA: the K bf16 activations at `x` (optionally RMS-normalised,
+// x * rsqrt(mean(x^2) + eps) * norm_w rounded to bf16) become, in shared memory, f16 values
+// scaled by a power of two 2^e that puts the largest magnitude in [2^14, 2^15) (elements 2, 3,
+// 6, 7 of every eight by a further 2^-4), plus (C2, T) per group of 128 for the main loop
+// (gemv_w4a16_m1.cuh explains the arithmetic).  Returns 2^-e.
+//
+// Measured: 2 to 3.5 us per phase on 768 threads, of which about 1 us is the instruction fetch
+// of code that the weight loop evicted in between (a second call right after the first takes
+// 1.5 to 2 us).  Calling it once on stale data while the CTA waits at the grid barrier, to warm
+// the instruction cache, was tried (hence the barrier id and thread count arguments): the dry
+// call outlasts the barrier wait, and the step got slower (2.17 against 2.03 ms).
+__device__ __forceinline__ float ps_prologue(const __nv_bfloat16 *x, const float *norm_w, int K, float eps, uint32_t xs0,
+                                          uint32_t gs0, float2 *warp_part, int tid, int bar_id, int bar_count) {
+    const int warp = tid >> 5, lane = tid & 31;
+    const uint4 *x4 = reinterpret_cast<const uint4 *>(x);
+    const int nvec = K >> 3;  // a multiple of 32: the guards below are uniform per warp
+    {
+        uint4 xv[PS_NV];
+#pragma unroll
+        for (int it = 0; it < PS_NV; ++it) {
+            const int i = tid + it * PS_THREADS;
+            if (i < nvec) xv[it] = __ldcg(x4 + i);
+        }
+#pragma unroll
+        for (int it = 0; it < PS_NV; ++it) {
+            const int i = tid + it * PS_THREADS;
+            if (i < nvec)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(xs0 + i * 16), "r"(xv[it].x), "r"(xv[it].y),
+                             "r"(xv[it].z), "r"(xv[it].w)
+                             : "memory");
+        }
+    }
+    // pass 1: sum of squares and largest magnitude (each thread re-reads what it stored)
+    float ss = 0.f, amax = 0.f;
+#pragma unroll 1
+    for (int i = tid; i < nvec; i += PS_THREADS) {
+        const uint4 v = lds128(xs0 + i * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        if (norm_w) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i);
+            const float4 w1 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i + 1);
+            const float nw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xffff0000u);
+                ss = fmaf(f0, f0, ss);
+                ss = fmaf(f1, f1, ss);
+                amax = fmaxf(amax, fmaxf(fabsf(f0 * nw[2 * j]), fabsf(f1 * nw[2 * j + 1])));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j] & 0xffff0000u))));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    }
+    if (lane == 0) warp_part[warp] = make_float2(ss, amax);
+    ps_bar(bar_id, bar_count);
+    {
+        const float2 t = lane < PS_WARPS ? warp_part[lane] : make_float2(0.f, 0.f);
+        ss = t.x;
+        amax = t.y;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        }
+    }
+    float inv = 1.f;
+    if (norm_w) {
+        inv = rsqrtf(fmaf(ss, 1.0f / (float)K, eps));  // within 2 ulp of the separately rounded form
+        amax = amax * inv * 1.0078125f;                // bound on |bf16(x inv w)|
+    }
+    int e = 141 - (int)((__float_as_uint(amax) >> 23) & 0xffu);
+    e = max(-100, min(100, e));
+    const float sc_lo = __uint_as_float((uint32_t)(e + 127) << 23);
+    const float sc_hi = __uint_as_float((uint32_t)(e - 4 + 127) << 23);
+
+    // pass 2: f16 copy (in place) and group sums
+#pragma unroll 1
+    for (int i = tid; i < nvec; i += PS_THREADS) {
+        const uint4 v = lds128(xs0 + i * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        float nw[8];
+        if (norm_w) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i);
+            const float4 w1 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i + 1);
+            nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w;
+            nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
+        }
+        uint32_t h[4];
+        float p = 0.f, sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xffff0000u);
+            if (norm_w) {
+                f0 = bf16_round(__fmul_rn(__fmul_rn(f0, inv), nw[2 * j]));
+                f1 = bf16_round(__fmul_rn(__fmul_rn(f1, inv), nw[2 * j + 1]));
+            }
+            const float sc = (j & 1) ? sc_hi : sc_lo;  // words 1 and 3 hold elements 2,3 and 6,7
+            const __half2 hh = __floats2half2_rn(f0 * sc, f1 * sc);
+            h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+            const float2 back = __half22float2(hh);
+            p += back.x + back.y;
+            sum += f0 + f1;
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(xs0 + i * 16), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3])
+                     : "memory");
+        // a group is 16 consecutive vectors = 16 consecutive lanes
+        const uint32_t half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            p += __shfl_xor_sync(half_mask, p, o);
+            sum += __shfl_xor_sync(half_mask, sum, o);
+        }
+        if ((lane & 15) == 0) {
+            const float T = sum * sc_lo;
+            const float C2 = 1024.f * p - 128.f * T;
+            asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(gs0 + (i >> 4) * 8), "f"(C2), "f"(T) : "memory");
+        }
+    }
+    ps_bar(bar_id, bar_count);
+    return __uint_as_float((uint32_t)(127 - e) << 23);
+}
+
+template <bool TRACE>
 __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(const PsArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float2 warp_part[PS_WARPS];
@@ -215,7 +376,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
         }
     };
     next_range();
-#pragma unroll
+#pragma unroll 1
     for (int j = 0; j < PS_STAGES; ++j) refill(ring0 + j * PS_BLOCK_BYTES, bar0 + j * 8);
 
     // ---- attention geometry: the same in every block (one sequence, one new token)
@@ -235,7 +396,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
     // phase timestamps of the first, the middle and the last CTA (thread 0 of each)
     const int trace_slot = blockIdx.x == 0 ? 0 : (blockIdx.x == gridDim.x / 2 ? 1 : (blockIdx.x == gridDim.x - 1 ? 2 : -1));
     auto stamp = [&](int oi, int which) {
-        if (trace_slot >= 0 && tid == 0) a.trace[((size_t)trace_slot * a.nops + oi) * 4 + which] = mbar_wall_ns();
+        if (TRACE && trace_slot >= 0 && tid == 0) a.trace[((size_t)trace_slot * a.nops + oi) * PS_TRACE + which] = mbar_wall_ns();
     };
 
     for (int oi = 0; oi < a.nops; ++oi) {
@@ -271,106 +432,8 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
             if (tid < PS_LOCAL_TILES) cta_cnt[tid] = 0;
           if (ntile > 0) {  // a CTA without tiles of this projection has nothing to prepare
 
-            // ---- prologue, pass 1: sum of squares and largest magnitude ----------
-            const uint4 *x4 = reinterpret_cast<const uint4 *>(op.x);
-            const int nvec = K >> 3;
-            uint4 xv[PS_NV];
-            float ss = 0.f, amax = 0.f;
-#pragma unroll
-            for (int it = 0; it < PS_NV; ++it) {
-                const int i = tid + it * PS_THREADS;
-                xv[it] = i < nvec ? __ldcg(x4 + i) : make_uint4(0u, 0u, 0u, 0u);
-                const uint32_t w[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
-                float nw[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
-                if (norm_w && i < nvec) {
-                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i);
-                    const float4 w1 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i + 1);
-                    nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w;
-                    nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xffff0000u);
-                    ss = fmaf(f0, f0, ss);
-                    ss = fmaf(f1, f1, ss);
-                    amax = fmaxf(amax, fmaxf(fabsf(f0 * nw[2 * j]), fabsf(f1 * nw[2 * j + 1])));
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            }
-            if (lane == 0) warp_part[warp] = make_float2(ss, amax);
-            __syncthreads();
-            {
-                const float2 t = lane < PS_WARPS ? warp_part[lane] : make_float2(0.f, 0.f);
-                ss = t.x;
-                amax = t.y;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                }
-            }
-            float inv = 1.f;
-            if (norm_w) {
-                inv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), a.eps)));
-                amax = amax * inv * 1.0078125f;  // bound on |bf16(x inv w)|
-            }
-            int e = 141 - (int)((__float_as_uint(amax) >> 23) & 0xffu);
-            e = max(-100, min(100, e));
-            const float sc_lo = __uint_as_float((uint32_t)(e + 127) << 23);
-            const float sc_hi = __uint_as_float((uint32_t)(e - 4 + 127) << 23);
-            const float unscale = __uint_as_float((uint32_t)(127 - e) << 23);
-
-            // ---- prologue, pass 2: f16 copy and group sums -------------------------
-#pragma unroll
-            for (int it = 0; it < PS_NV; ++it) {
-                const int i = tid + it * PS_THREADS;
-                if (i < nvec) {  // uniform over each aligned group of 16 lanes (nvec is a multiple of 16)
-                    const uint32_t w[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
-                    float nw[8];
-                    if (norm_w) {
-                        const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i);
-                        const float4 w1 = __ldg(reinterpret_cast<const float4 *>(norm_w) + 2 * i + 1);
-                        nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w;
-                        nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
-                    }
-                    uint32_t h[4];
-                    float p = 0.f, sum = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xffff0000u);
-                        if (norm_w) {
-                            f0 = bf16_round(__fmul_rn(__fmul_rn(f0, inv), nw[2 * j]));
-                            f1 = bf16_round(__fmul_rn(__fmul_rn(f1, inv), nw[2 * j + 1]));
-                        }
-                        const float sc = (j & 1) ? sc_hi : sc_lo;  // words 1 and 3 hold elements 2,3 and 6,7
-                        const __half2 hh = __floats2half2_rn(f0 * sc, f1 * sc);
-                        h[j] = *reinterpret_cast<const uint32_t *>(&hh);
-                        const float2 back = __half22float2(hh);
-                        p += back.x + back.y;
-                        sum += f0 + f1;
-                    }
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(xs0 + i * 16), "r"(h[0]), "r"(h[1]),
-                                 "r"(h[2]), "r"(h[3])
-                                 : "memory");
-                    const uint32_t half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
-#pragma unroll
-                    for (int o = 8; o > 0; o >>= 1) {
-                        p += __shfl_xor_sync(half_mask, p, o);
-                        sum += __shfl_xor_sync(half_mask, sum, o);
-                    }
-                    if ((lane & 15) == 0) {
-                        const float T = sum * sc_lo;
-                        const float C2 = 1024.f * p - 128.f * T;
-                        asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(gs0 + (i >> 4) * 8), "f"(C2), "f"(T)
-                                     : "memory");
-                    }
-                }
-            }
-            __syncthreads();
+            // ---- prologue (one shared instance of the code: see ps_prologue)
+            const float unscale = ps_prologue(op.x, norm_w, K, a.eps, xs0, gs0, warp_part, tid, 0, PS_THREADS);
             stamp(oi, 1);
 
             // ---- main loop: this warp's blocks ------------------------------------
@@ -382,16 +445,19 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
             const int epi = op.epi;
 
             int lt = b0 / G, g = b0 - lt * G;  // tile of the CTA, group
+
             uint4 xw[4];
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) xw[wi] = make_uint4(0u, 0u, 0u, 0u);
 
-            for (int b = b0; b < b1 && !dead && !(a.debug & 1);) {
+#pragma unroll 1
+            for (int b = b0; b < b1 && !dead;) {
                 const int n = min(G - g, b1 - b);
                 const bool whole = n == G;
                 float acc_a = 0.f, acc_b = 0.f;
                 uint32_t xaddr = xlane + g * 256, gaddr = gs0 + g * 8;
 
+#pragma unroll 1
                 for (int it = 0; it < n; ++it) {
                     if (!mbar_wait_addr(bar, parity)) {
                         if (lane == 0) atomicExch(a.status, (int)AB2_ERR_TIMEOUT);
@@ -447,12 +513,13 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                 float va = acc_a * unscale, vb = acc_b * unscale;
                 bool store = whole;
                 if (!whole) {
-                    // contributors: the warps of this CTA whose ranges meet [lt*G, lt*G + G)
-                    const int cut = rem * (base + 1);
-                    const int first_b = lt * G, last_b = first_b + G - 1;
-                    const int w_first = first_b < cut ? first_b / (base + 1) : rem + (first_b - cut) / base;
-                    const int w_last = last_b < cut ? last_b / (base + 1) : rem + (last_b - cut) / base;
-                    const int which = warp == w_first ? 1 : 0;  // slot 1: the tile my range ends inside
+                    // The tile is shared with other warps of this CTA: the warps whose ranges meet
+                    // [lt*G, lt*G + G).  Each leaves its partial in a slot (slot 1: the tile its range
+                    // ends inside) and bumps the tile's counter; the last to arrive sums the slots in
+                    // warp order (= block order), so the result does not depend on arrival order.
+                    const int w_first = ps_warp_of_block(lt * G, base, rem);
+                    const int w_last = ps_warp_of_block(lt * G + G - 1, base, rem);
+                    const int which = warp == w_first ? 1 : 0;
                     if (c == 0) cta_part[warp][which][r] = make_float2(va, vb);
                     __threadfence_block();
                     __syncwarp();
@@ -462,21 +529,24 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                     store = arrived == w_last - w_first;
                     if (store) {
                         __threadfence_block();
-                        float sum_a = 0.f, sum_b = 0.f;
-                        for (int w = w_first; w <= w_last; ++w) {  // contributor order: the sum does not depend on arrival order
+                        va = 0.f;
+                        vb = 0.f;
+#pragma unroll 1
+                        for (int w = w_first; w <= w_last; ++w) {
                             const float2 v = cta_part[w][w == w_first ? 1 : 0][r];
-                            sum_a += v.x;
-                            sum_b += v.y;
+                            va += v.x;
+                            vb += v.y;
                         }
-                        va = sum_a;
-                        vb = sum_b;
                     }
                 }
                 const int tile = tile_lo + lt;
                 if (store && c == 0) {
                     if (epi == W4_EPI_SWIGLU) {
                         const int col = tile * 8 + r;
-                        if (col < (N >> 1)) y[col] = __float2bfloat16_rn(swiglu_value(bf16_round(va), bf16_round(vb)));
+                        if (col < (N >> 1)) {  // silu(gate) * up on the rounded projections; fast exp / divide (1e-6 relative)
+                            const float gt = bf16_round(va);
+                            y[col] = __float2bfloat16_rn(__fdividef(gt, 1.0f + __expf(-gt)) * bf16_round(vb));
+                        }
                     } else {
 #pragma unroll
                         for (int hh = 0; hh < 2; ++hh) {
@@ -492,10 +562,11 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                 g = 0;
                 ++lt;
             }
+            stamp(oi, 7);  // warp 0 is through its blocks
           }  // ntile > 0
         } else if (kind == PS_ATTN) {
             const int nsplit = a.nsplit, rep = a.rep, kvh = a.kv.kvh;
-            if (att_on && !(a.debug & 2)) {
+            if (att_on) {
                 PsAttnSmem &S = *reinterpret_cast<PsAttnSmem *>(act_ptr);
                 const int kvhead = att_kvhead, rank = att_rank;
                 constexpr int half = PS_HD / 2;
@@ -576,61 +647,62 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                     S.newv[half + 2 * lane] = vd[2]; S.newv[half + 2 * lane + 1] = vd[3];
                 }
                 __syncthreads();
+                stamp(oi, 4);
 
-                // ---- scores: a warp per token, a lane per four dimensions
+                // ---- scores: a warp per token, a lane per four dimensions.  Loops are kept rolled:
+                // this code runs once per block and is fetched cold each time, so its length counts.
                 {
-                    float4 q4[4];
-#pragma unroll
-                    for (int hh = 0; hh < 4; ++hh)
-                        q4[hh] = hh < rep ? *reinterpret_cast<const float4 *>(&S.qs[hh][lane * 4]) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int t0 = warp; t0 < ntok; t0 += 2 * PS_WARPS) {
-                        float kf[2][4], ksv[2], vsv[2];
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {  // two tokens of the warp in flight at once
-                            const int t = t0 + u * PS_WARPS;
-                            if (t < ncached) {
-                                const size_t trow = head_base + c0 + t;
-                                i8x4_to_f32(*reinterpret_cast<const uint32_t *>(kc + trow * PS_HD + lane * 4), kf[u]);
-                                ksv[u] = ksc[trow];
-                                vsv[u] = vsc[trow];
-                            } else {  // the new token, already dequantised (or nothing)
-                                const float4 nk = *reinterpret_cast<const float4 *>(&S.newk[lane * 4]);
-                                kf[u][0] = nk.x; kf[u][1] = nk.y; kf[u][2] = nk.z; kf[u][3] = nk.w;
-                                ksv[u] = 1.f;
-                                vsv[u] = 1.f;
-                            }
+                    // the next token's row is requested before the current one is reduced
+                    auto fetch = [&](int t, uint32_t &kraw, float &ksv, float &vsv) {
+                        kraw = 0u; ksv = 1.f; vsv = 1.f;
+                        if (t < ncached) {
+                            const size_t trow = head_base + c0 + t;
+                            kraw = __ldg(reinterpret_cast<const uint32_t *>(kc + trow * PS_HD + lane * 4));
+                            ksv = __ldg(ksc + trow);
+                            vsv = __ldg(vsc + trow);
                         }
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            const int t = t0 + u * PS_WARPS;
-                            float dot[4];
-#pragma unroll
-                            for (int hh = 0; hh < 4; ++hh) {
-                                dot[hh] = q4[hh].x * kf[u][0];
-                                dot[hh] = fmaf(q4[hh].y, kf[u][1], dot[hh]);
-                                dot[hh] = fmaf(q4[hh].z, kf[u][2], dot[hh]);
-                                dot[hh] = fmaf(q4[hh].w, kf[u][3], dot[hh]);
-#pragma unroll
-                                for (int o = 16; o > 0; o >>= 1) dot[hh] += __shfl_xor_sync(0xffffffffu, dot[hh], o);
-                            }
-                            if (t < ntok) {
-                                const float dv = lane == 0 ? dot[0] : lane == 1 ? dot[1] : lane == 2 ? dot[2] : dot[3];
-                                if (lane < 4) S.sc[t][lane] = dv * ksv[u] * a.scale;
-                                if (lane == 4) S.vscale[t] = vsv[u];
-                            }
+                    };
+                    uint32_t kraw_n;
+                    float ks_n, vs_n;
+                    fetch(warp, kraw_n, ks_n, vs_n);
+#pragma unroll 1
+                    for (int t = warp; t < ntok; t += PS_WARPS) {
+                        const uint32_t kraw = kraw_n;
+                        const float ksv = ks_n, vsv = vs_n;
+                        fetch(t + PS_WARPS, kraw_n, ks_n, vs_n);
+                        float kf[4];
+                        i8x4_to_f32(kraw, kf);
+                        if (t >= ncached) {  // the new token, already dequantised
+                            const float4 nk = *reinterpret_cast<const float4 *>(&S.newk[lane * 4]);
+                            kf[0] = nk.x; kf[1] = nk.y; kf[2] = nk.z; kf[3] = nk.w;
                         }
+#pragma unroll 1
+                        for (int hh = 0; hh < rep; ++hh) {
+                            const float4 q = *reinterpret_cast<const float4 *>(&S.qs[hh][lane * 4]);
+                            float dot = q.x * kf[0];
+                            dot = fmaf(q.y, kf[1], dot);
+                            dot = fmaf(q.z, kf[2], dot);
+                            dot = fmaf(q.w, kf[3], dot);
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                            if (lane == 0) S.sc[t][hh] = dot * ksv * a.scale;
+                        }
+                        if (lane == 0) S.vscale[t] = vsv;
                     }
                 }
                 __syncthreads();
+                stamp(oi, 5);
                 // ---- softmax within the CTA: warp hh normalises head hh
                 if (warp < rep) {
                     float m = -INFINITY;
+#pragma unroll 1
                     for (int t = lane; t < ntok; t += 32) m = fmaxf(m, S.sc[t][warp]);
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
                     float l = 0.f;
+#pragma unroll 1
                     for (int t = lane; t < ntok; t += 32) {
-                        const float p = expf(S.sc[t][warp] - m);
+                        const float p = __expf(S.sc[t][warp] - m);
                         l += p;
                         S.sc[t][warp] = p * S.vscale[t];
                     }
@@ -639,80 +711,74 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                     if (lane == 0) { S.hm[warp] = m; S.hl[warp] = l; }
                 }
                 __syncthreads();
-                // ---- P.V: warp = (token subset, head), a lane per four dimensions
+                stamp(oi, 6);
+                // ---- P.V: warp = (token subset, head), a lane per four dimensions; four tokens in flight
                 {
                     const int hh = warp % rep, ts = warp / rep, nts = PS_WARPS / rep;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
                     for (int t0 = ts; t0 < ntok; t0 += 4 * nts) {
                         uint32_t raw[4];
-                        float pv[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
-                            const int t = t0 + u * nts;
-                            raw[u] = 0u;
-                            pv[u] = 0.f;
-                            if (t < ncached) {
-                                raw[u] = *reinterpret_cast<const uint32_t *>(vc + (head_base + c0 + t) * PS_HD + lane * 4);
-                                pv[u] = S.sc[t][hh];
-                            }
+                            const int t = min(t0 + u * nts, max(ncached - 1, 0));
+                            raw[u] = __ldg(reinterpret_cast<const uint32_t *>(vc + (head_base + c0 + t) * PS_HD + lane * 4));
                         }
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             const int t = t0 + u * nts;
                             float vf[4];
                             i8x4_to_f32(raw[u], vf);
-                            if (t >= ncached && t < ntok) {  // the new token
+                            if (t >= ncached && t < ntok) {  // the new token (past the end the clamped row stands, times 0)
                                 const float4 nv = *reinterpret_cast<const float4 *>(&S.newv[lane * 4]);
                                 vf[0] = nv.x; vf[1] = nv.y; vf[2] = nv.z; vf[3] = nv.w;
-                                pv[u] = S.sc[t][hh];
                             }
+                            const float pv = t < ntok ? S.sc[t][hh] : 0.f;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) acc[j] = fmaf(pv[u], vf[j], acc[j]);
+                            for (int j = 0; j < 4; ++j) acc[j] = fmaf(pv, vf[j], acc[j]);
                         }
                     }
                     *reinterpret_cast<float4 *>(&S.pacc[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
                 }
                 __syncthreads();
+                stamp(oi, 7);
                 // ---- this CTA's partial -> global memory
                 const size_t pbase = ((size_t)kvhead * nsplit + rank) * rep;
                 for (int i = tid; i < rep * PS_HD; i += PS_THREADS) {
                     const int hh = i / PS_HD, d = i % PS_HD;
                     float A = 0.f;
+#pragma unroll 1
                     for (int ts = 0; ts < PS_WARPS / rep; ++ts) A += S.pacc[ts * rep + hh][d];
                     a.apart_acc[(pbase + hh) * PS_HD + d] = A;
-                    if (d == 0) {
-                        a.apart_ml[(pbase + hh) * 2] = S.hm[hh];
-                        a.apart_ml[(pbase + hh) * 2 + 1] = S.hl[hh];
-                    }
+                    if (d == 0) *reinterpret_cast<float2 *>(&a.apart_ml[(pbase + hh) * 2]) = make_float2(S.hm[hh], S.hl[hh]);
                 }
                 __threadfence();
                 __syncthreads();
                 if (tid == 0) s_last = atomicAdd(&a.acount[kvhead], 1) == nsplit - 1 ? 1 : 0;
                 __syncthreads();
+                stamp(oi, 8);
                 if (s_last) {
                     // the last CTA of the head to arrive merges the splits (log-sum-exp)
                     __threadfence();
+                    if (tid < rep * nsplit) {
+                        const int hh = tid / nsplit, s2 = tid % nsplit;
+                        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(&a.apart_ml[(((size_t)kvhead * nsplit + s2) * rep + hh) * 2]));
+                        S.mlbuf[hh][s2][0] = ml.x;
+                        S.mlbuf[hh][s2][1] = ml.y;
+                    }
+                    __syncthreads();
                     for (int i = tid; i < rep * PS_HD; i += PS_THREADS) {
                         const int hh = i / PS_HD, d = i % PS_HD;
-                        // every load of the thread is in flight before the first is used (at most 16 splits)
-                        float mv[16], lv[16], av[16];
-#pragma unroll
-                        for (int s2 = 0; s2 < 16; ++s2) {
-                            const size_t pb = ((size_t)kvhead * nsplit + min(s2, nsplit - 1)) * rep + hh;
-                            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(&a.apart_ml[pb * 2]));
-                            mv[s2] = s2 < nsplit ? ml.x : -INFINITY;
-                            lv[s2] = ml.y;
-                            av[s2] = __ldcg(&a.apart_acc[pb * PS_HD + d]);
-                        }
                         float M = -INFINITY;
-#pragma unroll
-                        for (int s2 = 0; s2 < 16; ++s2) M = fmaxf(M, mv[s2]);
+#pragma unroll 1
+                        for (int s2 = 0; s2 < nsplit; ++s2) M = fmaxf(M, S.mlbuf[hh][s2][0]);
                         float L = 0.f, A = 0.f;
-#pragma unroll
-                        for (int s2 = 0; s2 < 16; ++s2) {
-                            const float e2 = (mv[s2] == -INFINITY) ? 0.f : expf(mv[s2] - M);
-                            L += e2 * lv[s2];
-                            A += e2 * av[s2];
+                        const float *accp = a.apart_acc + ((size_t)kvhead * nsplit * rep + hh) * PS_HD + d;
+#pragma unroll 4
+                        for (int s2 = 0; s2 < nsplit; ++s2) {
+                            const float e2 = __expf(S.mlbuf[hh][s2][0] - M);  // exp(-inf) = 0 for an empty split
+                            L = fmaf(e2, S.mlbuf[hh][s2][1], L);
+                            A = fmaf(e2, __ldcg(accp + (size_t)s2 * rep * PS_HD), A);
                         }
                         a.attn[(size_t)(kvhead * rep + hh) * PS_HD + d] = __float2bfloat16_rn(L > 0.f ? A * (1.0f / L) : A);
                     }
@@ -753,23 +819,23 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
         // ---- grid barrier: the next phase reads what this one wrote ------------------
         if (oi + 1 < a.nops) {
             ++barrier_no;
-            // what the next phase reads and this launch never writes is pulled into L1 while the
+            // what the next phase reads and this launch never writes is pulled into L2 while the
             // CTA waits: the RMSNorm weight, or the cached K / V rows of this CTA's tokens
             {
                 const PsOp &nx = ops[oi + 1];
                 if (nx.kind == PS_GEMV && nx.norm_w) {
                     for (int i = tid; i < nx.K >> 5; i += PS_THREADS)
-                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(nx.norm_w + (size_t)i * 32));
+                        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(nx.norm_w + (size_t)i * 32));
                 } else if (nx.kind == PS_ATTN && att_ncached > 0) {
                     const size_t layer_off = (size_t)nx.layer * a.kv_layer_tokens;
                     const size_t trow0 = layer_off + att_head_base + att_c0;
                     if (tid < att_ncached) {
-                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"((const int8_t *)a.kv.k + (trow0 + tid) * PS_HD));
-                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"((const int8_t *)a.kv.v + (trow0 + tid) * PS_HD));
+                        asm volatile("prefetch.global.L2 [%0];\n" ::"l"((const int8_t *)a.kv.k + (trow0 + tid) * PS_HD));
+                        asm volatile("prefetch.global.L2 [%0];\n" ::"l"((const int8_t *)a.kv.v + (trow0 + tid) * PS_HD));
                     }
                     if (tid * 32 < att_ncached) {  // scale words: 32 per line
-                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(a.kv.ks + trow0 + tid * 32));
-                        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(a.kv.vs + trow0 + tid * 32));
+                        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(a.kv.ks + trow0 + tid * 32));
+                        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(a.kv.vs + trow0 + tid * 32));
                     }
                 }
             }
@@ -824,6 +890,7 @@ struct PersistentStep {
     unsigned int bar_total = 0;  // arrivals the barrier word has seen once every launch so far has finished
     int max_tiles = 0, recovery_epoch = 0;
     unsigned long long *trace = nullptr;
+    bool traced = false;
 };
 
 static bool ps_weight_ok(const ab2_qweight *w) {
@@ -832,8 +899,10 @@ static bool ps_weight_ok(const ab2_qweight *w) {
 
 int persistent_step_create(PersistentStep **out, const PsModelDesc &d) {
     *out = nullptr;
-    static const bool off = getenv("AB2_NO_PERSISTENT_STEP") != nullptr;
-    if (off) return AB2_OK;
+    // Opt-in (AB2_PERSISTENT_STEP=1, read when a model is finalised): on the Large-class decoder the
+    // graph-replayed chain of kernels is still the faster of the two (1.82 against 1.98 ms per step).
+    const char *on = getenv("AB2_PERSISTENT_STEP");
+    if (!on || on[0] == '0') return AB2_OK;
     if (d.head_dim != PS_HD || d.n_heads % d.n_kv_heads != 0) return AB2_OK;
     const int rep = d.n_heads / d.n_kv_heads;
     if (rep != 1 && rep != 2 && rep != 4) return AB2_OK;
@@ -849,12 +918,13 @@ int persistent_step_create(PersistentStep **out, const PsModelDesc &d) {
     const int nops_of_model = 1 + 5 * d.n_layers + 2;
     const size_t smem = ps_smem_bytes(nops_of_model);
     if (smem > 220 * 1024) return AB2_OK;  // too many blocks for the shared copy of the op list
-    if (cudaFuncSetAttribute(decode_step_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(decode_step_persistent_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_step_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return AB2_OK;
     }
     int per_sm = 0;
-    AB2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_persistent_kernel, PS_THREADS, smem));
+    AB2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_persistent_kernel<true>, PS_THREADS, smem));
     if (per_sm < 1) return AB2_OK;
     const int grid = device_sm_count();
     if (d.n_kv_heads > grid) return AB2_OK;
@@ -903,8 +973,8 @@ int persistent_step_create(PersistentStep **out, const PsModelDesc &d) {
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->apart_ml, parts * 2 * sizeof(float));
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->acount, (size_t)d.n_kv_heads * sizeof(int));
     if (err == cudaSuccess) err = cudaMemset(ps->acount, 0, (size_t)d.n_kv_heads * sizeof(int));
-    if (err == cudaSuccess) err = cudaMalloc((void **)&ps->trace, (size_t)3 * ops.size() * 4 * sizeof(unsigned long long));
-    if (err == cudaSuccess) err = cudaMemset(ps->trace, 0, (size_t)3 * ops.size() * 4 * sizeof(unsigned long long));
+    if (err == cudaSuccess) err = cudaMalloc((void **)&ps->trace, (size_t)3 * ops.size() * PS_TRACE * sizeof(unsigned long long));
+    if (err == cudaSuccess) err = cudaMemset(ps->trace, 0, (size_t)3 * ops.size() * PS_TRACE * sizeof(unsigned long long));
     if (err == cudaSuccess) err = cudaMalloc((void **)&ps->bar, sizeof(unsigned int));
     if (err == cudaSuccess) err = cudaMemset(ps->bar, 0, sizeof(unsigned int));
     if (err == cudaSuccess) err = cudaDeviceSynchronize();
@@ -926,10 +996,11 @@ void persistent_step_destroy(PersistentStep *ps) {
 
 int persistent_step_trace(const PersistentStep *ps, unsigned long long *out, int capacity, int *nphases) {
     AB2_REQUIRE(ps && out && nphases, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(ps->traced, AB2_ERR_UNSUPPORTED, "phase timestamps are recorded only when AB2_PS_TRACE is set in the environment");
     *nphases = ps->nops;
-    AB2_REQUIRE(capacity >= 3 * ps->nops * 4, AB2_ERR_CAPACITY, "the trace needs room for %d values", 3 * ps->nops * 4);
+    AB2_REQUIRE(capacity >= 3 * ps->nops * PS_TRACE, AB2_ERR_CAPACITY, "the trace needs room for %d values", 3 * ps->nops * PS_TRACE);
     AB2_CUDA(cudaDeviceSynchronize());
-    AB2_CUDA(cudaMemcpy(out, ps->trace, (size_t)3 * ps->nops * 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    AB2_CUDA(cudaMemcpy(out, ps->trace, (size_t)3 * ps->nops * PS_TRACE * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return AB2_OK;
 }
 
@@ -969,8 +1040,6 @@ int persistent_step_launch(PersistentStep *ps, ab2_kv *kv, const uint32_t *ids_d
     a.status = status;
     a.logits = (__nv_bfloat16 *)logits_dev; a.vocab = d.vocab; a.argmax_out = argmax_dev;
     a.trace = ps->trace;
-    static const int debug = getenv("AB2_PS_DEBUG") ? atoi(getenv("AB2_PS_DEBUG")) : 0;
-    a.debug = debug;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ps->grid); cfg.blockDim = dim3(PS_THREADS);
@@ -979,7 +1048,11 @@ int persistent_step_launch(PersistentStep *ps, ab2_kv *kv, const uint32_t *ids_d
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_step_persistent_kernel, a);
+    // AB2_PS_TRACE=1 runs the build of the kernel that records phase timestamps (ab2_model_step_trace)
+    static const bool trace = getenv("AB2_PS_TRACE") != nullptr;
+    ps->traced = trace;
+    cudaError_t e = trace ? cudaLaunchKernelEx(&cfg, decode_step_persistent_kernel<true>, a)
+                          : cudaLaunchKernelEx(&cfg, decode_step_persistent_kernel<false>, a);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(AB2_ERR_CUDA, "persistent decode step launch failed: %s", cudaGetErrorString(e));

@@ -36,8 +36,9 @@ bool persistent_step_serves(const PersistentStep *ps, const ab2_kv *kv, int len_
 int persistent_step_launch(PersistentStep *ps, ab2_kv *kv, const uint32_t *ids_dev, int row, void *logits_dev,
                            uint32_t *argmax_dev, cudaStream_t s);
 
-// Timestamps (ns, GPU wall clock) of the last step: [3 CTAs: first, middle, last][phase][4] =
-// phase start, prologue done, CTA done, barrier passed.
+// Timestamps (ns, GPU wall clock) of the last step: [3 CTAs: first, middle, last][phase][10];
+// entries 0..3 = phase start, prologue done, CTA done, barrier passed; 4..9 = points inside the
+// phase (0 where a phase has none).
 int persistent_step_trace(const PersistentStep *ps, unsigned long long *out, int capacity, int *nphases);
 
 }  // namespace ab2

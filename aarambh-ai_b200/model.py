@@ -125,12 +125,13 @@ class AarambhModel:
 
     def step_trace(self):
         """Phase timestamps (ns) of the last persistent one-row decode step as an int64
-        array [3 CTAs, phases, 4]: phase start, prologue done, CTA done, barrier passed."""
+        array [3 CTAs, phases, 10]: phase start, prologue done, CTA done, barrier passed, then
+        up to six points inside the phase (0 where unused)."""
         import numpy as np
         n = C.c_int(0)
-        buf = np.zeros(3 * 4096 * 4, np.uint64)
+        buf = np.zeros(3 * 4096 * 10, np.uint64)
         check(lib.ab2_model_step_trace(self._h, buf.ctypes.data, buf.size, C.byref(n)))
-        return buf[:3 * n.value * 4].astype(np.int64).reshape(3, n.value, 4)
+        return buf[:3 * n.value * 10].astype(np.int64).reshape(3, n.value, 10)
 
     def __del__(self):
         try:

@@ -336,11 +336,14 @@ int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int
                           void *logits_dev, uint32_t *argmax_dev, ab2_stream stream);
 /* Profiling aid (no counterpart in the reference): when the last one-row decode step ran as
  * the single persistent kernel, copies the GPU wall-clock timestamps (ns) of its phases to
- * values_host as [3 CTAs: first, middle, last][phase][4] = {phase start, prologue done,
- * CTA done, grid barrier passed}; phases are embedding, then per block {qkv, attention, o,
+ * values_host as [3 CTAs: first, middle, last][phase][10]: entries 0..3 = {phase start,
+ * prologue done, CTA done, grid barrier passed}, 4..9 = points inside the phase (0 where a
+ * phase has none); phases are embedding, then per block {qkv, attention, o,
  * gate|up, down}, the LM head, and the tail (argmax, length commit).  *nphases receives the
- * phase count; AB2_ERR_UNSUPPORTED when the model does not use that kernel, AB2_ERR_CAPACITY
- * when `capacity` (in values) is less than 12 * phases.  Synchronises the device. */
+ * phase count.  The timestamps are recorded only by processes started with AB2_PS_TRACE set in
+ * the environment (the default build of the kernel carries no probes); AB2_ERR_UNSUPPORTED
+ * otherwise or when the model does not use that kernel, AB2_ERR_CAPACITY
+ * when `capacity` (in values) is less than 30 * phases.  Synchronises the device. */
 int ab2_model_step_trace(const ab2_model *m, unsigned long long *values_host, int capacity, int *nphases);
 
 #ifdef __cplusplus

@@ -422,6 +422,37 @@ ORC_API void orc_linear_f32(const float *x, const float *w, float *y, int M, int
     }
 }
 
+/* The same contraction as a SIMD GEMV would run it: 32 independent partial sums per
+ * output (two vector registers of lanes), lanes added at the end.
+ * The reference's CPU path calls Candle's matmul, which lands in the `gemm` crate's
+ * SIMD micro-kernels (crates/aarambh-studio-quant/src/qat.rs:323; gemm 0.19 is not
+ * vendored); their exact summation order is not published, so this form is not a
+ * parity definition - it brackets the SPEED of that path next to the strict-order
+ * loop above, and is used only by the timed CPU baseline.  Results differ from
+ * orc_linear_f32 by summation order only. */
+typedef float orc_v16 __attribute__((vector_size(64), aligned(4), may_alias));
+__attribute__((target_clones("arch=skylake-avx512", "arch=haswell", "default")))
+static float orc_dot_lanes(const float *x, const float *w, int K) {
+    orc_v16 acc0 = {0}, acc1 = {0};
+    int k = 0;
+    for (; k + 32 <= K; k += 32) {
+        acc0 += *(const orc_v16 *)(x + k) * *(const orc_v16 *)(w + k);
+        acc1 += *(const orc_v16 *)(x + k + 16) * *(const orc_v16 *)(w + k + 16);
+    }
+    float sum = 0.0f;
+    for (int j = 0; j < 16; ++j) sum += acc0[j] + acc1[j];
+    for (; k < K; ++k) sum += x[k] * w[k];
+    return sum;
+}
+
+ORC_API void orc_linear_f32_lanes(const float *x, const float *w, float *y, int M, int N, int K) {
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n) {
+        const float *wr = w + (size_t)n * K;
+        for (int m = 0; m < M; ++m) y[(size_t)m * N + n] = orc_dot_lanes(x + (size_t)m * K, wr, K);
+    }
+}
+
 /* Same contraction with f64 accumulation, used only to report how far both the
  * f32 oracle and the GPU are from the exact answer. */
 ORC_API void orc_linear_f64acc(const float *x, const float *w, float *y, int M, int N, int K) {
@@ -667,6 +698,7 @@ typedef struct {
     float **kc, **vc;
     int *lens; /* [batch] committed length per sequence */
     int norm_simd_order; /* 1: AVX2+FMA summation order (simd_norm.rs:246-284) */
+    int linear_lanes;    /* 1: projections in 16-lane SIMD order (timed baseline only) */
 } orc_model;
 
 ORC_API orc_model *orc_model_create(int n_layers, int d_model, int n_heads, int n_kv_heads,
@@ -676,7 +708,7 @@ ORC_API orc_model *orc_model_create(int n_layers, int d_model, int n_heads, int 
     m->n_layers = n_layers; m->d_model = d_model; m->n_heads = n_heads;
     m->n_kv_heads = n_kv_heads; m->head_dim = head_dim; m->ffn_hidden = ffn_hidden;
     m->vocab = vocab; m->max_seq = max_seq; m->eps = eps; m->rope_theta = rope_theta;
-    m->batch = batch; m->cap = cap; m->norm_simd_order = 1;
+    m->batch = batch; m->cap = cap; m->norm_simd_order = 1; m->linear_lanes = 0;
     size_t L = (size_t)n_layers;
     m->wq = calloc(L, sizeof(float *)); m->wk = calloc(L, sizeof(float *));
     m->wv = calloc(L, sizeof(float *)); m->wo = calloc(L, sizeof(float *));
@@ -711,6 +743,12 @@ ORC_API void orc_model_set_weight(orc_model *m, int layer, int which, const floa
 }
 
 ORC_API void orc_model_set_norm_order(orc_model *m, int simd_order) { m->norm_simd_order = simd_order; }
+/* 0: strict k order per output (the parity definition); 1: 16-lane SIMD order (timed baseline only). */
+ORC_API void orc_model_set_linear_order(orc_model *m, int lanes) { m->linear_lanes = lanes; }
+static void model_linear(const orc_model *m, const float *x, const float *w, float *y, int M, int N, int K) {
+    if (m->linear_lanes) orc_linear_f32_lanes(x, w, y, M, N, K);
+    else orc_linear_f32(x, w, y, M, N, K);
+}
 
 ORC_API void orc_model_reset(orc_model *m) {
     for (int b = 0; b < m->batch; ++b) m->lens[b] = 0;
@@ -789,9 +827,9 @@ ORC_API int orc_model_forward(orc_model *m, const uint32_t *ids, int B, int S, i
 
     for (int l = 0; l < m->n_layers; ++l) {
         model_norm(m, x, m->norm1[l], xn, (int)T);
-        orc_linear_f32(xn, m->wq[l], qb, (int)T, h * hd, d);
-        orc_linear_f32(xn, m->wk[l], kb, (int)T, kvh * hd, d);
-        orc_linear_f32(xn, m->wv[l], vb, (int)T, kvh * hd, d);
+        model_linear(m, xn, m->wq[l], qb, (int)T, h * hd, d);
+        model_linear(m, xn, m->wk[l], kb, (int)T, kvh * hd, d);
+        model_linear(m, xn, m->wv[l], vb, (int)T, kvh * hd, d);
         for (int b = 0; b < B; ++b) {
             int row = row0 + b, off = offsets[b], len0 = m->lens[row];
             orc_rope_apply(qb + (size_t)b * S * h * hd, qr + (size_t)b * S * h * hd, m->cos_t,
@@ -831,18 +869,18 @@ ORC_API int orc_model_forward(orc_model *m, const uint32_t *ids, int B, int S, i
                 }
             }
         }
-        orc_linear_f32(att, m->wo[l], proj, (int)T, d, h * hd);
+        model_linear(m, att, m->wo[l], proj, (int)T, d, h * hd);
         for (long i = 0; i < T * d; ++i) x[i] = x[i] + proj[i];
         model_norm(m, x, m->norm2[l], xn, (int)T);
-        orc_linear_f32(xn, m->w_gate[l], gate, (int)T, ffn, d);
-        orc_linear_f32(xn, m->w_up[l], up, (int)T, ffn, d);
+        model_linear(m, xn, m->w_gate[l], gate, (int)T, ffn, d);
+        model_linear(m, xn, m->w_up[l], up, (int)T, ffn, d);
         orc_swiglu(gate, up, hid, (size_t)T * ffn);
-        orc_linear_f32(hid, m->w_down[l], proj, (int)T, d, ffn);
+        model_linear(m, hid, m->w_down[l], proj, (int)T, d, ffn);
         for (long i = 0; i < T * d; ++i) x[i] = x[i] + proj[i];
     }
     for (int b = 0; b < B; ++b) m->lens[row0 + b] += S;
     model_norm(m, x, m->final_norm, xn, (int)T);
-    orc_linear_f32(xn, m->lm_head, logits, (int)T, V, d);
+    model_linear(m, xn, m->lm_head, logits, (int)T, V, d);
     free(x); free(xn); free(qb); free(qr); free(kb); free(kr); free(vb); free(att);
     free(proj); free(gate); free(up); free(hid);
     return 0;

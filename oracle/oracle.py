@@ -87,6 +87,7 @@ def _declare(L):
     L.orc_model_create.restype = C.c_void_p
     L.orc_model_set_weight.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p]
     L.orc_model_set_norm_order.argtypes = [C.c_void_p, C.c_int]
+    L.orc_model_set_linear_order.argtypes = [C.c_void_p, C.c_int]
     L.orc_model_reset.argtypes = [C.c_void_p]
     L.orc_model_seq_len.argtypes = [C.c_void_p, C.c_int]; L.orc_model_seq_len.restype = C.c_int
     L.orc_model_truncate.argtypes = [C.c_void_p, C.c_int, C.c_int]
@@ -438,6 +439,11 @@ class DenseModel:
         if rc != 0:
             raise ValueError("KV cache capacity or max_seq_len exceeded")
         return logits
+
+    def set_linear_order(self, lanes: bool):
+        """False: strict k order per output (the parity definition); True: 16-lane SIMD
+        order with FMA, for the timed CPU baseline only."""
+        lib().orc_model_set_linear_order(self.h, 1 if lanes else 0)
 
     def fill_cache(self, row, length, seed=1):
         lib().orc_model_fill_cache(self.h, row, length, seed)

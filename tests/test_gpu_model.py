@@ -233,3 +233,41 @@ def test_batched_decode_step_over_ragged_long_rows_matches_oracle():
         for b in range(B):
             assert rel_err(got[b], refs[b][lens[b] + s]) < 2e-2, (s, b)
     assert pkg().device_status() == 0
+
+
+@pytest.mark.parametrize("prompt_len", [5, 300, 510])
+def test_persistent_decode_step_matches_oracle(prompt_len, monkeypatch):
+    """The opt-in form of the one-row decode step (AB2_PERSISTENT_STEP=1 when the model is
+    finalised): one cooperative kernel for the whole step.  Same comparison as the
+    graph-replayed step: logits against the dense f32 oracle over the whole sequence, the
+    greedy token against the argmax of the returned logits, the cache length advanced on
+    the device; without AB2_PS_TRACE the phase trace is refused."""
+    p = pkg()
+    monkeypatch.setenv("AB2_PERSISTENT_STEP", "1")
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
+               max_seq=1024)
+    gpu, cpu, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=640, capacity=640)
+    steps = 4
+    ids = prompt(cfg["vocab"], prompt_len + steps, 7)
+    ref = cpu.forward(ids[None], [0])[0]
+    cache = gpu.empty_kv_cache_with_capacity(prompt_len + steps + 2, dtype="int8")
+    gpu.forward_with_cache(ids[None, :prompt_len], 0, cache)
+    side = torch.cuda.Stream()
+    logits = torch.empty((1, cfg["vocab"]), dtype=torch.bfloat16, device="cuda")
+    tok = torch.empty(1, dtype=torch.int32, device="cuda")
+    out = torch.empty(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for s in range(steps):
+        pos = prompt_len + s
+        with torch.cuda.stream(side):
+            tok.fill_(int(ids[pos]))
+            gpu.decode_step(tok, cache, logits, out)
+            side.synchronize()
+        got = logits.float().cpu().numpy()[0]
+        assert rel_err(got, ref[pos]) < 2e-2, (prompt_len, s)
+        assert int(out[0]) == orc.argmax(got)
+        assert cache.seq_len() == pos + 1
+    assert p.device_status() == 0
+    with pytest.raises(p.Ab2Error) as e:
+        gpu.step_trace()
+    assert e.value.status == -7
