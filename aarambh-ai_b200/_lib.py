@@ -101,6 +101,8 @@ SIGNATURES = {
     "ab2_model_forward": ([_p, _p, _p, _i, _i, _i, _p, _i, _p, _p, _p], _i),
     "ab2_model_decode_step": ([_p, _p, _p, _i, _i, _p, _p, _p], _i),
     "ab2_model_step_trace": ([_p, _p, _i, _p], _i),
+    "ab2_model_forward_rows": ([_p, _p, _p, _i, _p, _i, _i, _p, _p, _p], _i),
+    "ab2_model_decode_step_rows": ([_p, _p, _p, _p, _i, _p, _p, _p], _i),
 }
 
 

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(AttnArgs a) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x, kvhead = blockIdx.y;
-    const int rrow = blockIdx.z / a.S, qi = blockIdx.z % a.S, row = a.row0 + rrow;
+    const int rrow = blockIdx.z / a.S, qi = blockIdx.z % a.S, row = kv_row(a.kv, a.row0, rrow);
     const int kv_end = a.kv.lens[row] + a.pending - a.S + qi + 1;
     int per = (kv_end + a.nsplit - 1) / a.nsplit;
     per = (per + 31) & ~31;
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(AttnArgs a) {
 __global__ void attn_merge_kernel(AttnArgs a, int HD) {
     pdl_wait();  // inputs come from the preceding kernel of the step
     pdl_launch_dependents();
-    const int head = blockIdx.x, rrow = blockIdx.y, row = a.row0 + rrow, d = threadIdx.x;
+    const int head = blockIdx.x, rrow = blockIdx.y, row = kv_row(a.kv, a.row0, rrow), d = threadIdx.x;
     const size_t p0 = ((size_t)row * a.h + head) * a.nsplit;
     float M = -INFINITY;
     for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, a.part_ml[(p0 + s) * 2]);
@@ -292,7 +292,7 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
     a.dtype = (int)dtype; a.scale = scale; a.part_acc = kv->part_acc; a.part_ml = kv->part_ml;
     int max_len = len_hint;
     if (max_len <= 0)
-        for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + pending);
+        for (int i = 0; i < nrows; ++i) max_len = std::max(max_len, kv->lens_host[kv_row_host(kv, row0, i)] + pending);
     int nsplit = 1;
     if (S == 1 && decode_on_mma(kv) && st.q_h == kv->hd && st.o_h == st.q_h && st.o_b == (long long)kv->h * kv->hd) {
         // INT8 cache, head_dim 128: tensor-core flash-decode (attention_mma.cu)

@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) attn_decode_cluster_kernel(ClusterArgs a)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int rank = (int)cluster_rank(), nsplit = a.nsplit;
-    const int kvhead = blockIdx.y, rrow = blockIdx.z, row = a.row0 + rrow;
+    const int kvhead = blockIdx.y, rrow = blockIdx.z, row = kv_row(a.kv, a.row0, rrow);
     constexpr int half = HD / 2;
     const int pos = a.kv.lens[row];                       // cached tokens; the new one lands here
     const int rpos = a.rope_pos ? a.rope_pos[row] : pos;  // RoPE position of the new token

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(FusedArgs a) {
     __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    const int split = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = a.row0 + rrow;
+    const int split = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = kv_row(a.kv, a.row0, rrow);
     const int half = HD / 2;
     const int pos = a.kv.lens[row];                       // cached tokens; the new one lands here
     const int rpos = a.rope_pos ? a.rope_pos[row] : pos;  // RoPE position of the new token
@@ -447,7 +447,7 @@ int attention_decode_fused_device(ab2_kv *kv, int layer, const void *qkv, long l
     a.part_acc = kv->part_acc; a.part_ml = kv->part_ml; a.counters = kv->counters;
     int max_len = len_hint;
     if (max_len <= 0)
-        for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r]);
+        for (int i = 0; i < nrows; ++i) max_len = std::max(max_len, kv->lens_host[kv_row_host(kv, row0, i)]);
     const int want = (2 * device_sm_count() + nrows * kv->kvh - 1) / (nrows * kv->kvh);
     a.nsplit = std::max(1, std::min(std::min(want, (max_len + 127) / 128), kv->max_splits));
     dim3 grid(a.nsplit, kv->kvh, nrows);

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(MmaAttnArgs a) {
     pdl_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
-    const int split = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = a.row0 + rrow;
+    const int split = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = kv_row(a.kv, a.row0, rrow);
     const int len = a.kv.lens[row] + a.pending;
     int per = (len + a.nsplit - 1) / a.nsplit;
     per = (per + 63) & ~63;  // whole 16-token blocks for each of the four warps

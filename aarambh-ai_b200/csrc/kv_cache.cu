@@ -34,7 +34,7 @@ __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T 
     pdl_wait();  // inputs come from the preceding kernel of the step
     pdl_launch_dependents();
     const int hd = kv.hd, half = hd >> 1;
-    const int s = blockIdx.x, head = blockIdx.y, rrow = blockIdx.z, row = row0 + rrow;
+    const int s = blockIdx.x, head = blockIdx.y, rrow = blockIdx.z, row = kv_row(kv, row0, rrow);
     const int d = threadIdx.x;
     if (head >= kv.kvh) {
         // blocks past the KV heads rotate one query head in place (same row stride as k / v)
@@ -102,9 +102,9 @@ __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T 
     }
 }
 
-__global__ void kv_advance_kernel(int *lens, int row0, int nrows, int S) {
+__global__ void kv_advance_kernel(int *lens, const int *rows, int row0, int nrows, int S) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < nrows) lens[row0 + i] += S;
+    if (i < nrows) lens[rows ? rows[row0 + i] : row0 + i] += S;
 }
 
 // Dequantised contents of one sequence in the reference layout [len][kvh][hd].
@@ -140,6 +140,7 @@ KvView kv_view(const ab2_kv *kv, int layer) {
     v.ks = kv->ks ? kv->ks + (size_t)layer * tokens : nullptr;
     v.vs = kv->vs ? kv->vs + (size_t)layer * tokens : nullptr;
     v.lens = kv->lens_dev;
+    v.rows = kv->rows_on ? kv->rows_dev : nullptr;
     return v;
 }
 
@@ -173,9 +174,9 @@ int kv_append_device(ab2_kv *kv, int layer, const void *k, const void *v, long l
 }
 
 int kv_commit_device(ab2_kv *kv, int S, int row0, int nrows, cudaStream_t s) {
-    kv_advance_kernel<<<(nrows + 127) / 128, 128, 0, s>>>(kv->lens_dev, row0, nrows, S);
+    kv_advance_kernel<<<(nrows + 127) / 128, 128, 0, s>>>(kv->lens_dev, kv->rows_on ? kv->rows_dev : nullptr, row0, nrows, S);
     AB2_LAUNCH_CHECK();
-    for (int r = row0; r < row0 + nrows; ++r) kv->lens_host[r] += S;
+    for (int i = 0; i < nrows; ++i) kv->lens_host[kv_row_host(kv, row0, i)] += S;
     return AB2_OK;
 }
 
@@ -209,6 +210,8 @@ AB2_API int ab2_kv_create(ab2_kv **out, int n_layers, int batch, int capacity, i
     if (e == cudaSuccess) e = cudaMalloc((void **)&kv->lens_dev, (size_t)batch * 4);
     if (e == cudaSuccess) e = cudaMemset(kv->lens_dev, 0, (size_t)batch * 4);
     if (e == cudaSuccess) e = cudaMallocHost((void **)&kv->lens_host, (size_t)batch * 4);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&kv->rows_dev, (size_t)batch * 4);
+    if (e == cudaSuccess) e = cudaMallocHost((void **)&kv->rows_host, (size_t)batch * 4);
     // split-context scratch: partial accumulators and (max, sum) pairs
     kv->max_splits = AB2_KV_MAX_SPLITS;
     size_t nparts = (size_t)batch * n_heads * kv->max_splits;
@@ -230,6 +233,8 @@ AB2_API int ab2_kv_destroy(ab2_kv *kv) {
     cudaFree(kv->k); cudaFree(kv->v); cudaFree(kv->ks); cudaFree(kv->vs); cudaFree(kv->lens_dev);
     cudaFree(kv->part_acc); cudaFree(kv->part_ml); cudaFree(kv->counters);
     if (kv->lens_host) cudaFreeHost(kv->lens_host);
+    cudaFree(kv->rows_dev);
+    if (kv->rows_host) cudaFreeHost(kv->rows_host);
     delete kv;
     return AB2_OK;
 }

@@ -17,6 +17,11 @@ struct ab2_kv {
     float *part_ml;   // [B][h][max_splits][2]  (running max, running sum)
     int max_splits;
     int *counters;    // [B][kvh] split-arrival counters of the fused decode attention (zero at rest)
+    // Row selection: while `rows_on` is set, row index i of a call addresses cache row rows[i]
+    // (an arbitrary set of live sequences served in one pass); otherwise rows are row0 + i.
+    int *rows_dev;    // [B]
+    int *rows_host;   // [B], pinned
+    bool rows_on;
 };
 
 namespace ab2 {
@@ -26,7 +31,16 @@ struct KvView {
     void *k, *v;
     float *ks, *vs;
     int *lens;
+    const int *rows;  // selected cache rows of this call, or null (rows are row0 + i)
 };
+
+// Cache row addressed by index i of a call that starts at row0.
+__device__ __forceinline__ int kv_row(const KvView &kv, int row0, int i) {
+    return kv.rows ? kv.rows[row0 + i] : row0 + i;
+}
+static inline int kv_row_host(const ab2_kv *kv, int row0, int i) {
+    return kv->rows_on ? kv->rows_host[row0 + i] : row0 + i;
+}
 
 KvView kv_view(const ab2_kv *kv, int layer);
 

@@ -170,7 +170,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         else STEP(norm_linear(m, L.wqkv, xcur, L.norm1, T, m->qkv, 0, s));
         int max_len = len_hint;
         if (S == 1 && max_len <= 0)
-            for (int r = row0; r < row0 + nrows; ++r) max_len = std::max(max_len, kv->lens_host[r] + 1);
+            for (int i = 0; i < nrows; ++i) max_len = std::max(max_len, kv->lens_host[kv_row_host(kv, row0, i)] + 1);
         if (S == 1 && !decode_attention_on_tensor_cores(kv, nrows, max_len)) {
             // decode: RoPE, KV append, attention and split merge in one launch
             if (attention_decode_cluster_eligible(kv, m->dtype, max_len))
@@ -317,15 +317,22 @@ static int check_forward(ab2_model *m, ab2_kv *kv, const void *ids, int S, int r
                 "KV cache head layout does not match the model");
     AB2_REQUIRE(S > 0 && nrows > 0 && row0 >= 0 && row0 + nrows <= kv->B, AB2_ERR_BAD_SHAPE,
                 "rows %d..%d outside the cache batch %d", row0, row0 + nrows, kv->B);
+    for (int r = 0; r < nrows; ++r) {
+        const int row = kv_row_host(kv, row0, r);
+        AB2_REQUIRE(row >= 0 && row < kv->B, AB2_ERR_BAD_SHAPE, "selected row %d outside the cache batch %d", row, kv->B);
+        for (int q = 0; q < r; ++q)
+            AB2_REQUIRE(kv_row_host(kv, row0, q) != row, AB2_ERR_BAD_ARG, "cache row %d is selected twice", row);
+    }
     AB2_REQUIRE(nrows * S <= m->max_tokens, AB2_ERR_CAPACITY, "%d tokens exceed the model workspace of %d", nrows * S, m->max_tokens);
     AB2_REQUIRE(logits_mode >= 0 && logits_mode <= 2, AB2_ERR_BAD_ARG, "logits_mode must be 0, 1 or 2");
     AB2_REQUIRE(logits_mode == 0 || logits != nullptr, AB2_ERR_BAD_ARG, "logits buffer is null");
     for (int r = 0; r < nrows; ++r) {
-        int off = offsets_host ? offsets_host[r] : kv->lens_host[row0 + r];
+        const int crow = kv_row_host(kv, row0, r);
+        int off = offsets_host ? offsets_host[r] : kv->lens_host[crow];
         AB2_REQUIRE(off >= 0 && off + S <= c.max_seq, AB2_ERR_BAD_SHAPE,
                     "batch row %d offset %d exceeds max_seq_len %d", r, off, c.max_seq);
-        AB2_REQUIRE(kv->lens_host[row0 + r] + S <= kv->cap, AB2_ERR_CAPACITY, "KV cache length %d exceeds capacity %d",
-                    kv->lens_host[row0 + r] + S, kv->cap);
+        AB2_REQUIRE(kv->lens_host[crow] + S <= kv->cap, AB2_ERR_CAPACITY, "KV cache length %d exceeds capacity %d",
+                    kv->lens_host[crow] + S, kv->cap);
     }
     return AB2_OK;
 }
@@ -529,8 +536,9 @@ AB2_API int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev,
     const int *rope_base = kv->lens_dev;
     if (offsets_host) {
         bool same = true;
-        for (int r = 0; r < nrows; ++r) same = same && offsets_host[r] == kv->lens_host[row0 + r];
+        for (int r = 0; r < nrows; ++r) same = same && offsets_host[r] == kv->lens_host[kv_row_host(kv, row0, r)];
         if (!same) {
+            AB2_REQUIRE(!kv->rows_on, AB2_ERR_UNSUPPORTED, "a forward over selected rows takes the cache lengths as offsets");
             // explicit seqlen offsets that differ from the cache lengths
             AB2_CUDA(cudaStreamSynchronize(s));
             // the buffers hold max_tokens entries and nrows <= max_tokens: they are filled from
@@ -543,6 +551,38 @@ AB2_API int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev,
     rc = forward_launches(m, kv, ids_dev, S, row0, nrows, rope_base, logits_mode, logits_dev, argmax_dev, 0, s);
     if (rc != AB2_OK) return rc;
     return kv_commit_device(kv, S, row0, nrows, s);
+}
+
+// Selects `nrows` cache rows for the call that follows: the list goes to the cache's pinned
+// mirror and, in stream order, to the device copy the kernels read.
+static int select_rows(ab2_kv *kv, const int *rows_host, int nrows, cudaStream_t s) {
+    AB2_REQUIRE(kv && rows_host, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(nrows > 0 && nrows <= kv->B, AB2_ERR_BAD_SHAPE, "%d rows selected, the cache holds %d", nrows, kv->B);
+    // the pinned list may still be in flight to the device from the previous call on this stream
+    AB2_CUDA(cudaStreamSynchronize(s));
+    for (int i = 0; i < nrows; ++i) kv->rows_host[i] = rows_host[i];
+    AB2_CUDA(cudaMemcpyAsync(kv->rows_dev, kv->rows_host, (size_t)nrows * 4, cudaMemcpyHostToDevice, s));
+    kv->rows_on = true;
+    return AB2_OK;
+}
+
+AB2_API int ab2_model_forward_rows(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, const int *rows_host,
+                                   int nrows, int logits_mode, void *logits_dev, uint32_t *argmax_dev,
+                                   ab2_stream stream) {
+    int rc = select_rows(kv, rows_host, nrows, (cudaStream_t)stream);
+    if (rc != AB2_OK) return rc;
+    rc = ab2_model_forward(m, kv, ids_dev, S, 0, nrows, nullptr, logits_mode, logits_dev, argmax_dev, stream);
+    kv->rows_on = false;
+    return rc;
+}
+
+AB2_API int ab2_model_decode_step_rows(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, const int *rows_host,
+                                       int nrows, void *logits_dev, uint32_t *argmax_dev, ab2_stream stream) {
+    int rc = select_rows(kv, rows_host, nrows, (cudaStream_t)stream);
+    if (rc != AB2_OK) return rc;
+    rc = ab2_model_decode_step(m, kv, ids_dev, 0, nrows, logits_dev, argmax_dev, stream);
+    kv->rows_on = false;
+    return rc;
 }
 
 AB2_API int ab2_model_step_trace(const ab2_model *m, unsigned long long *values_host, int capacity, int *nphases) {
@@ -566,8 +606,8 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
     // The attention launch is shaped by the context length (splits, kernel choice), which a captured
     // launch cannot read: graphs are kept per power-of-two bound of the longest row.
     int longest = 1;
-    for (int r = row0; r < row0 + nrows; ++r) longest = std::max(longest, kv->lens_host[r] + 1);
-    if (nrows == 1 && m->persistent && persistent_step_serves(m->persistent, kv, longest)) {
+    for (int i = 0; i < nrows; ++i) longest = std::max(longest, kv->lens_host[kv_row_host(kv, row0, i)] + 1);
+    if (nrows == 1 && !kv->rows_on && m->persistent && persistent_step_serves(m->persistent, kv, longest)) {
         // one sequence: the whole step is one persistent kernel (no graph needed)
         void *lg = logits_dev ? logits_dev : m->gu;
         rc = persistent_step_launch(m->persistent, kv, ids_dev, row0, lg, argmax_dev, s);
@@ -582,7 +622,7 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
     int len_bound = 512;
     while (len_bound < longest) len_bound <<= 1;
     len_bound = std::min(len_bound, kv->cap);
-    auto key = std::make_tuple((const void *)kv, (const void *)ids_dev, row0, nrows, (const void *)logits_dev,
+    auto key = std::make_tuple((const void *)kv, (const void *)ids_dev, kv->rows_on ? -1 : row0, nrows, (const void *)logits_dev,
                                (const void *)argmax_dev, len_bound);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
@@ -609,6 +649,6 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
         it = m->graphs.emplace(key, sg).first;
     }
     AB2_CUDA(cudaGraphLaunch(it->second.exec, s));
-    for (int r = row0; r < row0 + nrows; ++r) kv->lens_host[r] += 1;
+    for (int i = 0; i < nrows; ++i) kv->lens_host[kv_row_host(kv, row0, i)] += 1;
     return AB2_OK;
 }

@@ -116,6 +116,28 @@ class AarambhModel:
                                     stream_ptr()))
         return out
 
+    def forward_decode_rows(self, token_ids, rows, cache: KVCache) -> torch.Tensor:
+        """One token for each of an arbitrary set of cache rows in ONE forward: ids [n, 1],
+        rows [n] distinct cache rows; positions are the rows' cache lengths -> logits [n, 1, vocab]."""
+        ids = self._ids(token_ids)
+        rows = [int(r) for r in rows]
+        if ids.shape[1] != 1 or ids.shape[0] != len(rows):
+            raise _lib.Ab2Error(-1, f"expected ids [{len(rows)}, 1], got {list(ids.shape)}")
+        n = len(rows)
+        out = torch.empty((n, 1, self.cfg.vocab_size), dtype=self.dtype, device="cuda")
+        check(lib.ab2_model_forward_rows(self._h, cache._h, ids.data_ptr(), 1, (C.c_int * n)(*rows), n, 1,
+                                         out.data_ptr(), None, stream_ptr()))
+        return out
+
+    def decode_step_rows(self, ids_dev: torch.Tensor, rows, cache: KVCache, logits: torch.Tensor | None,
+                         argmax_dev: torch.Tensor | None):
+        """Graph-replayed one-token step over an arbitrary set of cache rows (ids_dev [n] int32)."""
+        rows = [int(r) for r in rows]
+        n = len(rows)
+        check(lib.ab2_model_decode_step_rows(self._h, cache._h, ids_dev.data_ptr(), (C.c_int * n)(*rows), n,
+                                             logits.data_ptr() if logits is not None else None,
+                                             argmax_dev.data_ptr() if argmax_dev is not None else None, stream_ptr()))
+
     def decode_step(self, ids_dev: torch.Tensor, cache: KVCache, logits: torch.Tensor | None,
                     argmax_dev: torch.Tensor | None, row0: int = 0):
         """Graph-replayed one-token step; ids_dev [B] int32 is read on the device."""

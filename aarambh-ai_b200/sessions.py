@@ -7,9 +7,9 @@ verification forward of speculative decoding
 (crates/aarambh-studio-inference/src/speculative.rs:304-318,388-418).
 
 Sessions live in the rows of ONE batched KV cache; a decode pass over sessions
-with different lengths is one ``forward_decode_batch`` per run of adjacent rows
-(per-row offsets, one fused attention launch for the run), where the reference
-loops over rows.  Sampling here is greedy (last maximum, as ``argmax`` in
+with different lengths is ONE forward over the list of their rows, whatever rows
+they occupy (per-row lengths, one attention launch for all of them), where the
+reference loops over rows.  Sampling here is greedy (last maximum, as ``argmax`` in
 sampler.rs:217-224); text, tools and stochastic samplers stay with the caller.
 """
 from __future__ import annotations
@@ -97,19 +97,15 @@ class SessionEngine:
             if s.pending_token is None:
                 raise _lib.Ab2Error(-1, "session has no pending token for batched decode")
         ordered = sorted(sessions, key=lambda s: s.row)
-        run = [ordered[0]]
-        for s in ordered[1:] + [None]:
-            if s is not None and s.row == run[-1].row + 1:
-                run.append(s)
-                continue
-            ids = torch.tensor([[r.pending_token] for r in run])
-            offsets = [r.prompt_len + len(r.generated_ids) - 1 for r in run]
-            logits = self.model.forward_decode_batch(ids, offsets, self.cache, row0=run[0].row)
-            for i, r in enumerate(run):
-                r.next_logits = logits[i, 0]
-                r.pending_token = None
-            if s is not None:
-                run = [s]
+        for s in ordered:
+            expect = s.prompt_len + len(s.generated_ids) - 1
+            if self.cache.seq_len(s.row) != expect:
+                raise _lib.Ab2Error(-1, f"cache row {s.row} holds {self.cache.seq_len(s.row)} tokens, the session expects {expect}")
+        ids = torch.tensor([[s.pending_token] for s in ordered])
+        logits = self.model.forward_decode_rows(ids, [s.row for s in ordered], self.cache)
+        for i, s in enumerate(ordered):
+            s.next_logits = logits[i, 0]
+            s.pending_token = None
 
     def release(self, session: GenerationSession) -> None:
         """Gives the session's row back (its cached tokens are dropped)."""

@@ -334,6 +334,19 @@ int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, 
  * argmax_dev may be passed as the next ids_dev. */
 int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int row0, int nrows,
                           void *logits_dev, uint32_t *argmax_dev, ab2_stream stream);
+/* The same two calls over an arbitrary set of cache rows: row i of ids / logits / argmax belongs
+ * to cache row rows_host[i] (distinct rows, any order), positions are the rows' cache lengths.
+ * This is what the serving batcher does each tick - every live session advances in ONE
+ * forward whatever rows they occupy (decode_sessions over `session_indices`,
+ * crates/aarambh-studio-serve/src/batching.rs:439-452; InferenceEngine::decode_sessions,
+ * crates/aarambh-studio-inference/src/engine.rs:323-355).  The decode step keeps one graph per
+ * (row count, context bound): the graph reads the row list from the cache's device copy, which
+ * each call refreshes in stream order. */
+int ab2_model_forward_rows(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, const int *rows_host,
+                           int nrows, int logits_mode, void *logits_dev, uint32_t *argmax_dev,
+                           ab2_stream stream);
+int ab2_model_decode_step_rows(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, const int *rows_host,
+                               int nrows, void *logits_dev, uint32_t *argmax_dev, ab2_stream stream);
 /* Profiling aid (no counterpart in the reference): when the last one-row decode step ran as
  * the single persistent kernel, copies the GPU wall-clock timestamps (ns) of its phases to
  * values_host as [3 CTAs: first, middle, last][phase][10]: entries 0..3 = {phase start,

@@ -270,4 +270,4 @@ def test_persistent_decode_step_matches_oracle(prompt_len, monkeypatch):
     assert p.device_status() == 0
     with pytest.raises(p.Ab2Error) as e:
         gpu.step_trace()
-    assert e.value.status == -7
+    assert e.value.status == -8

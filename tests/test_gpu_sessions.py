@@ -1,42 +1,45 @@
 """Callers above the decoder: ragged batched decode of sessions that join and
-leave, chunked prefill, and the verification forward of speculative decoding -
-each against the same sequences run alone, token for token."""
+leave (every live session in ONE forward, whatever rows they occupy), chunked
+prefill, and the verification forward of speculative decoding - each against
+the oracle's dense f32 model running the same sequence alone: greedy tokens
+identical, logits within 1e-4 (f32 path) or 2e-2 (bf16 / INT8-KV path)."""
 import numpy as np
 import pytest
 import torch
 
 from helpers import pkg, rel_err
 from model_fixtures import SMALL, build_pair
+from oracle import oracle as orc
 
 pytestmark = pytest.mark.gpu
 
 
-def _alone(gpu, ids, new_tokens):
-    """Greedy tokens and per-step logits of one sequence on its own cache (one prefill, one-token steps)."""
-    p = pkg()
-    cache = gpu.empty_kv_cache_with_capacity(SMALL["max_seq"])
-    lg = gpu.forward_with_cache(torch.tensor([ids]), 0, cache, last_only=True).view(1, -1)
+def _alone(cpu, ids, new_tokens):
+    """Greedy tokens and per-step logits of one sequence on the oracle (one prefill, one-token steps)."""
+    cpu.reset()
+    lg = cpu.forward(np.array([ids]), [0])[0, -1]
     toks, logits = [], []
     for i in range(new_tokens):
-        logits.append(lg.float().cpu().numpy().ravel())
-        toks.append(int(p.dispatch.argmax(lg)[0]))
+        logits.append(lg.copy())
+        toks.append(orc.argmax(lg))
         if i + 1 < new_tokens:
-            lg = gpu.forward_decode_batch(torch.tensor([[toks[-1]]]), [len(ids) + i], cache).view(1, -1)
+            lg = cpu.forward(np.array([[toks[-1]]]), [len(ids) + i])[0, 0]
     return toks, logits
 
 
 def test_sessions_join_leave_and_decode_together():
     p = pkg()
-    gpu, _, _ = build_pair(SMALL, "int8_channel", capacity=64)
+    gpu, cpu, _ = build_pair(SMALL, "int8_channel", capacity=64)
     rng = np.random.default_rng(5)
     prompts = [rng.integers(0, SMALL["vocab"], n).tolist() for n in (3, 17, 9, 6)]
     new = [10, 6, 12, 5]
-    want = [_alone(gpu, ids, n) for ids, n in zip(prompts, new)]
+    want = [_alone(cpu, ids, n) for ids, n in zip(prompts, new)]
 
     eng = p.sessions.SessionEngine(gpu, max_batch=3, capacity=SMALL["max_seq"])
     got = {i: ([], []) for i in range(4)}
     live = {}
     waiting = [0, 1, 2, 3]
+    passes_with_a_gap = 0
     while waiting or live:
         while waiting and eng.free_rows:          # a fourth session joins when a row frees up
             i = waiting.pop(0)
@@ -47,7 +50,11 @@ def test_sessions_join_leave_and_decode_together():
             if s.is_finished():
                 eng.release(s)
                 del live[i]
+        rows = sorted(s.row for s in live.values())
+        if len(rows) > 1 and rows[-1] - rows[0] + 1 > len(rows):
+            passes_with_a_gap += 1                # e.g. rows {0, 2}: still one forward
         eng.decode_sessions(list(live.values()))
+    assert passes_with_a_gap > 0
     for i in range(4):
         assert got[i][0] == want[i][0], i
         for a, b in zip(got[i][1], want[i][1]):
@@ -63,9 +70,9 @@ def test_sessions_join_leave_and_decode_together():
 
 def test_speculative_verification_accepts_exactly_the_greedy_prefix():
     p = pkg()
-    gpu, _, _ = build_pair(SMALL, "int8_channel", capacity=64)
+    gpu, cpu, _ = build_pair(SMALL, "int8_channel", capacity=64)
     prompt = np.random.default_rng(9).integers(0, SMALL["vocab"], 8).tolist()
-    toks, logits = _alone(gpu, prompt, 9)          # toks[0] follows the prompt, toks[i+1] follows toks[i]
+    toks, logits = _alone(cpu, prompt, 9)          # toks[0] follows the prompt, toks[i+1] follows toks[i]
     cache = gpu.empty_kv_cache_with_capacity(SMALL["max_seq"])
     gpu.forward_with_cache(torch.tensor([prompt]), 0, cache, last_only=True)
     base = len(prompt)
@@ -81,3 +88,42 @@ def test_speculative_verification_accepts_exactly_the_greedy_prefix():
     assert accepted2 == 3 and nxt2 == toks[8]
     with pytest.raises(p.Ab2Error, match="expected"):
         p.sessions.verify_draft(gpu, cache, 0, base, toks[0], draft)
+
+
+@pytest.mark.parametrize("rows,lens", [([0, 2], [40, 7]), ([3, 1, 2], [300, 5, 64]), ([2], [20])])
+def test_rows_in_any_order_decode_in_one_pass_on_the_w4a16_path(rows, lens):
+    """Non-adjacent cache rows, in any order, through one forward (plain launches) and through
+    the graph-replayed step (bf16, W4A16 weights, INT8 KV, head_dim 128: the row list reaches the
+    append, the cluster / tensor-core attention and the length commit) against the oracle."""
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2, max_seq=512)
+    gpu, cpu, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=320, capacity=320)
+    steps = 3
+    seqs = [np.random.default_rng(50 + i).integers(0, cfg["vocab"], n + 2 * steps) for i, n in enumerate(lens)]
+    refs = []
+    for sq in seqs:
+        cpu.reset()
+        refs.append(cpu.forward(sq[None], [0])[0])
+    cache = gpu.empty_kv_cache_with_capacity(320, batch=4, dtype="int8")
+    for r, sq, n in zip(rows, seqs, lens):
+        gpu.forward_with_cache(sq[None, :n], 0, cache, row=r)
+    n_rows = len(rows)
+    side = torch.cuda.Stream()
+    logits = torch.empty((n_rows, cfg["vocab"]), dtype=torch.bfloat16, device="cuda")
+    tok = torch.empty(n_rows, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for s in range(2 * steps):
+        ids = [int(sq[n + s]) for sq, n in zip(seqs, lens)]
+        if s < steps:       # plain launches
+            got = gpu.forward_decode_rows(torch.tensor(ids).view(-1, 1), rows, cache)[:, 0].float().cpu().numpy()
+        else:               # graph-replayed steps
+            with torch.cuda.stream(side):
+                tok.copy_(torch.tensor(ids, dtype=torch.int32))
+                gpu.decode_step_rows(tok, rows, cache, logits, None)
+                side.synchronize()
+            got = logits.float().cpu().numpy()
+        for i, (r, n) in enumerate(zip(rows, lens)):
+            assert rel_err(got[i], refs[i][n + s]) < 2e-2, (s, r)
+            assert cache.seq_len(r) == n + s + 1
+    assert pkg().device_status() == 0
+    with pytest.raises(pkg().Ab2Error):
+        gpu.forward_decode_rows(torch.tensor([[1], [2]]), [1, 1], cache)     # a row selected twice
