@@ -327,6 +327,8 @@ int qlinear_w4a16_norm_peer(const ab2_qweight *w, const void *x, const float *no
 int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 bool qlinear_i8_stream_eligible(const ab2_qweight *w, ab2_dtype dtype, int M);
 int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
+bool qlinear_i8_tc_eligible(const ab2_qweight *w, ab2_dtype dtype, int M);
+int qlinear_i8_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {
     if (qlinear_w4a16_mma_eligible(w, dtype)) {
@@ -338,6 +340,8 @@ int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype
     }
     // INT8 weights, bf16 activations, a few tokens: the HBM-bound streaming GEMV
     if (qlinear_i8_stream_eligible(w, dtype, M)) return qlinear_i8_stream(w, x, M, y, s);
+    // more tokens: tcgen05 GEMM, the codes converted to bf16 on the way into the operand stages
+    if (qlinear_i8_tc_eligible(w, dtype, M)) return qlinear_i8_tc(w, x, M, y, s);
     return qlinear_generic(w, x, M, dtype, y, s);
 }
 

@@ -389,7 +389,7 @@ def main():
         ids_dev = torch.empty(B, dtype=torch.int32, device="cuda")
         out_dev = torch.empty(B, dtype=torch.int32, device="cuda")
         ids_host.copy_(state["bufs"][state["n"] % 2].cpu())
-        e2e_steps = max(8, args.steps // 4)
+        e2e_steps = max(32, args.steps // 2)
         for b in range(B):
             cache.truncate(PROMPT, b)
 

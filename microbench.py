@@ -96,9 +96,38 @@ def bench_gemv(pkg, args):
         del lins
 
 
+def random_int8(pkg, N, K, seed):
+    """N(0, 0.02) weights quantised to INT8 with one absmax scale per output channel."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn((N, K), generator=g, device="cuda") * 0.02
+    return pkg.QuantLinear.quantise(w, "int8_channel")
+
+
+def bench_gemv_int8(pkg, args):
+    stream = torch.cuda.Stream()
+    for K, N in SHAPES:
+        copies = 1 if args.profile else max(2, math.ceil(400e6 / (N * K)))
+        lins = [random_int8(pkg, N, K, 2 + i) for i in range(copies)]
+        for M in args.m:
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            if args.profile:
+                for _ in range(3):
+                    lins[0](x)
+                torch.cuda.synchronize()
+                print("profiled case", K, N, M)
+                return
+            t = time_graph(lambda: [lin(x) for lin in lins], 5, stream) / copies
+            byt = K * N + 4 * N + 2 * M * (K + N)
+            print(json.dumps({"kernel": "gemv_i8_stream_kernel" if M <= 8 else "gemm_i8_tc_kernel", "K": K, "N": N, "M": M,
+                              "us": round(t * 1e6, 2), "GBs": round(byt / t / 1e9, 1),
+                              "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}), flush=True)
+        del lins
+
+
 def bench_gemm(pkg, args):
-    for K, N in SHAPES[:3]:
-        lin = random_w4a16(pkg, N, K, 2)
+    int8 = getattr(args, "fmt", "w4a16") == "int8"
+    for K, N in (SHAPES if args.shape else SHAPES[:3]):
+        lin = random_int8(pkg, N, K, 2) if int8 else random_w4a16(pkg, N, K, 2)
         dense = lin.dequantise(torch.bfloat16)
         for M in args.m:
             x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
@@ -118,7 +147,7 @@ def bench_gemm(pkg, args):
             ref = x @ dense.T
             err = ((y.float() - ref.float()).abs().max() / ref.float().abs().max()).item()
             fl = 2.0 * M * K * N
-            print(json.dumps({"kernel": "gemm_w4a16_tc_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 1),
+            print(json.dumps({"kernel": "gemm_i8_tc_kernel" if int8 else "gemm_w4a16_tc_kernel", "K": K, "N": N, "M": M, "us": round(t * 1e6, 1),
                               "TFLOPs": round(fl / t / 1e12, 1), "frac_of_measured_bf16": round(fl / t / 1e12 / peak_tflops(), 3),
                               "rel_err_vs_dense_bf16": err}), flush=True)
 
@@ -216,6 +245,7 @@ def main():
     ap.add_argument("--cases", default=None)
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--shape", default=None, help="K,N: restrict gemv / gemm to one weight shape")
+    ap.add_argument("--fmt", default="w4a16", choices=["w4a16", "int8"], help="weight format of gemv / gemm")
     args = ap.parse_args()
     pkg = import_package()
     torch.cuda.set_device(0)
@@ -224,7 +254,7 @@ def main():
         SHAPES[:] = [(k, n)]
     if args.what == "gemv":
         args.m = [int(v) for v in (args.m or "1,4,16").split(",")]
-        bench_gemv(pkg, args)
+        (bench_gemv_int8 if args.fmt == "int8" else bench_gemv)(pkg, args)
     elif args.what == "gemm":
         args.m = [int(v) for v in (args.m or "512,2048,8192").split(",")]
         bench_gemm(pkg, args)
