@@ -38,9 +38,9 @@ int device_sm_count();
 namespace {
 
 constexpr int TC_STAGES = 4;          // operand-A (unpacked weight) stages of 64 K-elements
-constexpr int TC_MAX_XSTAGES = 8;     // operand-B (activation) stages: a ring of its own, 128 KB deep, because an
+constexpr int TC_MAX_XSTAGES = 6;     // operand-B (activation) stages: a ring of its own, 128 KB deep, because an
                                       // activation tile takes about three stage times to arrive from L2
-constexpr int TC_WSLOTS = 3;          // code ring slots (128 K each)
+constexpr int TC_WSLOTS = 2;          // code ring slots (128 channels x 128 K, 16 KB each)
 constexpr int TC_WSLOT_BYTES = 128 * 128;  // 128 channels x 128 codes
 constexpr int TC_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
 constexpr int TC_THREADS = 480;  // 1 weight producer, 1 MMA, 8 convert, 4 epilogue, 1 activation producer

@@ -23,14 +23,16 @@
 using namespace ab2;
 
 namespace ab2 {
+int device_sm_count();
 namespace {
 
 constexpr int I8S_WARPS = 8;
-constexpr int I8S_UNROLL = 4;   // chunks in flight per warp
+constexpr int I8S_UNROLL = 4;   // chunks in flight per warp (8 costs occupancy: 0.38 against 0.59 of HBM on 4096 x 14336)
 
 template <typename T>
 __device__ __forceinline__ void store_out(T *y, size_t i, float v) { y[i] = from_f32<T>(v); }
 
+template <int RT>  // 16-row tiles per CTA (the activation fragments of a chunk serve all of them)
 __global__ void __launch_bounds__(256)
 gemv_i8_stream_kernel(const int8_t *__restrict__ codes, const float *__restrict__ scales,
                       const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, int N, int K, int M) {
@@ -38,7 +40,7 @@ gemv_i8_stream_kernel(const int8_t *__restrict__ codes, const float *__restrict_
     __half *xs = reinterpret_cast<__half *>(smem_raw);                 // [M][K] f16, scaled
     __shared__ float tok_T[8], tok_unscale[8];
     __shared__ float warp_red[I8S_WARPS][8][2];
-    __shared__ float red[I8S_WARPS][16][8];
+    __shared__ float red[I8S_WARPS][16 * RT][8];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, c = lane & 3;
@@ -100,24 +102,32 @@ gemv_i8_stream_kernel(const int8_t *__restrict__ codes, const float *__restrict_
     }
 
     // ---- main loop: this warp's chunks of 64 columns ------------------------------
-    const int row_a = min(tile * 16 + r, N - 1), row_b = min(tile * 16 + r + 8, N - 1);
-    const int8_t *pa = codes + (size_t)row_a * K + c * 16;
-    const int8_t *pb = codes + (size_t)row_b * K + c * 16;
+    const int8_t *pa[RT], *pb[RT];
+#pragma unroll
+    for (int q = 0; q < RT; ++q) {
+        pa[q] = codes + (size_t)min((tile * RT + q) * 16 + r, N - 1) * K + c * 16;
+        pb[q] = codes + (size_t)min((tile * RT + q) * 16 + r + 8, N - 1) * K + c * 16;
+    }
     const int nchunks = K >> 6;
     const uint32_t xs_lane = smem_addr(xs) + (uint32_t)(r * K + c * 16) * 2;  // token r, this lane's 16 columns
     const uint32_t has_x = r < M ? 1u : 0u;
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    float d[RT][4];
+#pragma unroll
+    for (int q = 0; q < RT; ++q) d[q][0] = d[q][1] = d[q][2] = d[q][3] = 0.f;
     uint4 xw0 = make_uint4(0u, 0u, 0u, 0u), xw1 = make_uint4(0u, 0u, 0u, 0u);
-    for (int ch0 = warp; ch0 < nchunks; ch0 += I8S_WARPS * I8S_UNROLL) {
-        uint4 wa[I8S_UNROLL], wb[I8S_UNROLL];
+    for (int ch0 = warp; ch0 < nchunks; ch0 += I8S_WARPS * (I8S_UNROLL)) {
+        uint4 wa[I8S_UNROLL][RT], wb[I8S_UNROLL][RT];
 #pragma unroll
         for (int u = 0; u < I8S_UNROLL; ++u) {
             const int ch = ch0 + u * I8S_WARPS;
-            if (ch < nchunks) {
-                wa[u] = __ldcs(reinterpret_cast<const uint4 *>(pa + (size_t)ch * 64));
-                wb[u] = __ldcs(reinterpret_cast<const uint4 *>(pb + (size_t)ch * 64));
-            } else {
-                wa[u] = wb[u] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // -128 + 128: see below
+#pragma unroll
+            for (int q = 0; q < RT; ++q) {
+                if (ch < nchunks) {
+                    wa[u][q] = __ldcs(reinterpret_cast<const uint4 *>(pa[q] + (size_t)ch * 64));
+                    wb[u][q] = __ldcs(reinterpret_cast<const uint4 *>(pb[q] + (size_t)ch * 64));
+                } else {
+                    wa[u][q] = wb[u][q] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
         }
 #pragma unroll
@@ -126,27 +136,33 @@ gemv_i8_stream_kernel(const int8_t *__restrict__ codes, const float *__restrict_
             if (ch >= nchunks) break;
             lds128_if(has_x, xs_lane + ch * 128, xw0);
             lds128_if(has_x, xs_lane + ch * 128 + 16, xw1);
-            const uint32_t ua[4] = {wa[u].x ^ 0x80808080u, wa[u].y ^ 0x80808080u, wa[u].z ^ 0x80808080u, wa[u].w ^ 0x80808080u};
-            const uint32_t ub[4] = {wb[u].x ^ 0x80808080u, wb[u].y ^ 0x80808080u, wb[u].z ^ 0x80808080u, wb[u].w ^ 0x80808080u};
             const uint32_t xb[8] = {xw0.x, xw0.y, xw0.z, xw0.w, xw1.x, xw1.y, xw1.z, xw1.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                // word j = columns 4j .. 4j+3 of this lane's 16: pairs (0,1) and (2,3)
-                const uint32_t a0 = __byte_perm(ua[j], 0x64646464u, 0x4140), a2 = __byte_perm(ua[j], 0x64646464u, 0x4342);
-                const uint32_t a1 = __byte_perm(ub[j], 0x64646464u, 0x4140), a3 = __byte_perm(ub[j], 0x64646464u, 0x4342);
-                mma_f16_16816(d, a0, a1, a2, a3, xb[2 * j], xb[2 * j + 1]);
+            for (int q = 0; q < RT; ++q) {
+                const uint32_t ua[4] = {wa[u][q].x ^ 0x80808080u, wa[u][q].y ^ 0x80808080u, wa[u][q].z ^ 0x80808080u, wa[u][q].w ^ 0x80808080u};
+                const uint32_t ub[4] = {wb[u][q].x ^ 0x80808080u, wb[u][q].y ^ 0x80808080u, wb[u][q].z ^ 0x80808080u, wb[u][q].w ^ 0x80808080u};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    // word j = columns 4j .. 4j+3 of this lane's 16: pairs (0,1) and (2,3)
+                    const uint32_t a0 = __byte_perm(ua[j], 0x64646464u, 0x4140), a2 = __byte_perm(ua[j], 0x64646464u, 0x4342);
+                    const uint32_t a1 = __byte_perm(ub[j], 0x64646464u, 0x4140), a3 = __byte_perm(ub[j], 0x64646464u, 0x4342);
+                    mma_f16_16816(d[q], a0, a1, a2, a3, xb[2 * j], xb[2 * j + 1]);
+                }
             }
         }
     }
     // d[0], d[1]: row r, tokens 2c, 2c+1; d[2], d[3]: row r + 8
-    red[warp][r][2 * c] = d[0];
-    red[warp][r][2 * c + 1] = d[1];
-    red[warp][r + 8][2 * c] = d[2];
-    red[warp][r + 8][2 * c + 1] = d[3];
+#pragma unroll
+    for (int q = 0; q < RT; ++q) {
+        red[warp][q * 16 + r][2 * c] = d[q][0];
+        red[warp][q * 16 + r][2 * c + 1] = d[q][1];
+        red[warp][q * 16 + r + 8][2 * c] = d[q][2];
+        red[warp][q * 16 + r + 8][2 * c + 1] = d[q][3];
+    }
     __syncthreads();
-    if (tid < 128) {
+    if (tid < 128 * RT) {
         const int row = tid >> 3, tok = tid & 7;
-        const int n = tile * 16 + row;
+        const int n = tile * 16 * RT + row;
         if (tok < M && n < N) {
             float D = 0.f;
 #pragma unroll
@@ -171,12 +187,17 @@ int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaS
     AB2_CUDA(cudaGetDevice(&dev));
     AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
     if (!configured[dev]) {
-        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         configured[dev] = true;
     }
+    // two 16-row tiles per CTA once that still leaves every SM a few CTAs (the activations are staged per CTA)
     const int tiles = (w->N + 15) / 16;
-    cudaError_t e = launch_kernel(gemv_i8_stream_kernel, dim3(tiles), dim3(256), smem, s, (const int8_t *)w->codes,
-                                  (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
+    const bool two = false;  // measured: two tiles per CTA is slower at every shape (0.47 against 0.59 of HBM on 4096 x 14336)
+    cudaError_t e = two ? launch_kernel(gemv_i8_stream_kernel<2>, dim3((tiles + 1) / 2), dim3(256), smem, s, (const int8_t *)w->codes,
+                                        (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M)
+                        : launch_kernel(gemv_i8_stream_kernel<1>, dim3(tiles), dim3(256), smem, s, (const int8_t *)w->codes,
+                                        (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "INT8 GEMV launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
