@@ -97,6 +97,12 @@ SIGNATURES = {
     "ab2_tp_all_reduce": ([_p, _p, C.c_size_t, _i, _p], _i),
     "ab2_tp_peer_export": ([_p, C.c_size_t, _p], _i),
     "ab2_tp_peer_attach": ([_p, _p], _i),
+    "ab2_tp_peer_block": ([_p, _pp, _p], _i),
+    "ab2_tp_peer_attach_ptrs": ([_p, _p], _i),
+    "ab2_tp_set_wait_limit_ns": ([_p, C.c_ulonglong], _i),
+    "ab2_tp_peer_reset": ([_p], _i),
+    "ab2_tp_peer_deposit": ([_p, _p, C.c_size_t, _p], _i),
+    "ab2_tp_peer_reduce_add": ([_p, _p, C.c_size_t, _p], _i),
     "ab2_model_rope_tables": ([_p, _pp, _pp], _i),
     "ab2_model_forward": ([_p, _p, _p, _i, _i, _i, _p, _i, _p, _p, _p], _i),
     "ab2_model_decode_step": ([_p, _p, _p, _i, _i, _p, _p, _p], _i),

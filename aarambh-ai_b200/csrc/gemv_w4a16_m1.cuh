@@ -81,12 +81,13 @@ constexpr int W4M1_LOCAL_TILES = 64;  // cut tiles a CTA can finish through shar
 // registers between the two passes of the prologue (K <= 2048 * NV).
 //
 // PEER_IN (tensor parallel, with NORM): the input is the residual stream plus
-// the sum over ranks of the partial sums waiting in this rank's inbox of the
-// peer exchange (tp.cuh).  CTA 0 tells the peers that this rank's partial sums
-// are in place, every CTA waits (bounded) for the peers' signals, adds the
-// partials in rank order and rounds as the stand-alone reduce does; CTA 0 also
-// writes the new residual stream to `x_out` (not `x`: other CTAs still read it),
-// and the CTA that finishes its prologue last advances the exchange count.
+// the sum over ranks of the partial sums arriving in this rank's inbox of the
+// peer exchange (tp.cuh).  Every inbox word carries the number of its exchange,
+// so each thread simply waits (bounded) until the words it needs show the
+// current number, adds the partials in rank order and rounds as the stand-alone
+// reduce does; CTA 0 also writes the new residual stream to `x_out` (not `x`:
+// other CTAs still read it), and the CTA that finishes its prologue last
+// advances the exchange count.
 template <int EPI, int STAGES, int NV, bool NORM, bool PEER_IN = false>
 __global__ void __launch_bounds__(256, 3)
 gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__restrict__ x,
@@ -140,61 +141,22 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     pdl_wait();
     pdl_launch_dependents();
 
-    // ---- tensor parallel: meet the other ranks -------------------------------
-    const float *box = nullptr;
+    // ---- tensor parallel: the partial sums of every rank wait in this rank's inbox ----
+    const unsigned long long *box = nullptr;
     size_t box_stride = 0;
     int box_world = 0;
     uint32_t exchange = 0;
+    unsigned long long wait_limit = 0;
+    __shared__ int peer_failed;
     if (PEER_IN) {
-        __shared__ int peer_failed;
         const ab2_tp_peer_desc d = *peers;
         exchange = *d.epoch + 1;
         if (threadIdx.x == 0) peer_failed = 0;
-        __syncthreads();
-        // CTA 0 talks to the peers (system scope, over NVLink); the other CTAs wait for its
-        // word in local memory instead of all polling the peers' flags
-        if (blockIdx.x == 0) {
-            if ((int)threadIdx.x < d.world && (int)threadIdx.x != d.rank) {
-                const int p = threadIdx.x;
-                __threadfence_system();
-                asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(d.flags[p] + d.rank), "r"(exchange) : "memory");
-                const uint32_t *mine = d.flags[d.rank] + p;
-                bool ok = false;
-                const unsigned long long t0 = mbar_wall_ns();
-                for (int spin = 0;; ++spin) {
-                    uint32_t v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(mine) : "memory");
-                    if ((int32_t)(v - exchange) >= 0) { ok = true; break; }
-                    if ((spin & 63) == 63 && mbar_wall_ns() - t0 > 2000000000ull) break;  // two seconds
-                    __nanosleep(20);
-                }
-                if (!ok) peer_failed = 1;
-            }
-            __syncthreads();
-            if (threadIdx.x == 0 && !peer_failed)
-                asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(d.ready), "r"(exchange) : "memory");
-        } else {
-            if (threadIdx.x == 0) {
-                bool ok = false;
-                const unsigned long long t0 = mbar_wall_ns();
-                for (int spin = 0;; ++spin) {
-                    uint32_t v;
-                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(d.ready) : "memory");
-                    if ((int32_t)(v - exchange) >= 0) { ok = true; break; }
-                    if ((spin & 63) == 63 && mbar_wall_ns() - t0 > 3000000000ull) break;  // CTA 0's own limit plus a margin
-                    __nanosleep(20);
-                }
-                if (!ok) peer_failed = 1;
-            }
-            __syncthreads();
-        }
-        if (peer_failed) {
-            if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
-            return;
-        }
         box = d.inbox[d.rank] + (size_t)(exchange & 1u) * d.world * d.max_elems;
         box_stride = d.max_elems;
         box_world = d.world;
+        wait_limit = d.wait_limit_ns;
+        __syncthreads();
     }
 
     // ---- prologue, pass 1: sum of squares and largest magnitude ---------------
@@ -210,10 +172,15 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
             // residual + bf16(sum over ranks), element by element as the stand-alone reduce does
             float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int rk = 0; rk < box_world; ++rk) {
-                const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)rk * box_stride) + 2 * i);
-                const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)rk * box_stride) + 2 * i + 1);
-                sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
-                sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+                // every word carries its exchange number: wait (bounded) until this thread's eight have arrived
+                float pv[8];
+                if (!tp_ll_wait8(box + (size_t)rk * box_stride + 8 * (size_t)i, exchange, wait_limit, pv)) {
+                    peer_failed = 1;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) pv[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sum[j] += pv[j];
             }
             uint32_t w[4] = {xv[it].x, xv[it].y, xv[it].z, xv[it].w};
 #pragma unroll
@@ -251,6 +218,12 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     }
     if (lane == 0) warp_part[warp] = make_float2(ss, amax);
     __syncthreads();
+    if (PEER_IN && peer_failed) {
+        // a peer's sums did not arrive within the limit: record it and stop (the exchange count is
+        // left as it was; ab2_tp_peer_reset puts the ranks back in step)
+        if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+        return;
+    }
     {
         const float2 t = lane < W4W_WARPS ? warp_part[lane] : make_float2(0.f, 0.f);
         ss = t.x;

@@ -44,10 +44,12 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
     const ab2_tp_peer_desc *peers = nullptr;
     size_t peer_off = 0;
     int peer_world = 0;
+    uint32_t exchange = 0;
     if (EPI == W4_EPI_F32_PEER) {
         peers = reinterpret_cast<const ab2_tp_peer_desc *>(y);
         peer_world = peers->world;
-        peer_off = ((size_t)((*peers->epoch + 1) & 1u) * peer_world + peers->rank) * peers->max_elems;
+        exchange = *peers->epoch + 1;
+        peer_off = ((size_t)(exchange & 1u) * peer_world + peers->rank) * peers->max_elems;
     }
     // The residual may alias the output (the stream is updated in place), so loads left between
     // the stores could not be moved ahead of them: all residual values are read first.
@@ -86,7 +88,8 @@ __device__ __forceinline__ void w4w_store_tile(const float (&acc)[NT][4], int ti
                     if (EPI == W4_EPI_F32) {  // unrounded partial sum of a row-parallel shard
                         reinterpret_cast<float *>(y)[o] = v;
                     } else if (EPI == W4_EPI_F32_PEER) {  // the same, stored over NVLink with every rank
-                        for (int p = 0; p < peer_world; ++p) peers->inbox[p][peer_off + o] = v;
+                        const unsigned long long word = tp_ll_pack(v, exchange);  // the sum and its arrival signal in one store
+                        for (int p = 0; p < peer_world; ++p) tp_ll_store(peers->inbox[p] + peer_off + o, word);
                     } else {
                         if (EPI == W4_EPI_ADD)  // residual + bf16(projection), as residual + x does
                             v = rv[t][2 * h + i] + __bfloat162float(__float2bfloat16_rn(v));

@@ -11,15 +11,18 @@
 // The all-reduce of the decoder's row-parallel projections does not have to go
 // through NCCL: once the ranks have exchanged CUDA IPC handles
 // (ab2_tp_peer_export / ab2_tp_peer_attach), the projection kernel stores its f32
-// partial sums straight into every rank's inbox over NVLink, and one small
-// kernel per exchange signals the peers, waits (bounded) for their signals,
-// adds the partials in rank order and applies the residual.  Inboxes are
-// double-buffered by the parity of a per-rank exchange count kept in device
-// memory, so graph replays need no host-side sequence number.  Only plain
-// stores and loads touch peer memory.
+// partial sums straight into every rank's inbox over NVLink, each as one 8-byte
+// word {sum, exchange number}; the consumer (the next projection's prologue, or
+// one small kernel) waits (bounded) until the words it needs carry the current
+// exchange number, adds the partials in rank order and applies the residual -
+// no flag, no fence, no signal round trip.  Inboxes are double-buffered by the
+// parity of a per-rank exchange count kept in device memory, so graph replays
+// need no host-side sequence number.  Only plain stores and loads touch peer
+// memory.
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstddef>
 #include <cstring>
 
 #include "common.cuh"
@@ -79,18 +82,9 @@ int device_status_word(int **out);
 
 namespace {
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// One CTA.  The partial sums of exchange e = epoch + 1 sit in buffer e & 1 of
-// every inbox (stored there by the projection kernels that ran before this one
-// on each rank).  x += bf16(sum_r partial_r), summed in rank order on every rank.
+// The partial sums of exchange e = epoch + 1 arrive in buffer e & 1 of every inbox (stored there
+// by the projection kernels of each rank, or by tp_peer_deposit_kernel), every word tagged with
+// e.  x += bf16(sum_r partial_r), summed in rank order on every rank.
 __global__ void __launch_bounds__(256)
 tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc *desc, int *status) {
     __shared__ int failed;
@@ -100,63 +94,19 @@ tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc
     const uint32_t e = *d.epoch + 1;
     if (threadIdx.x == 0) failed = 0;
     __syncthreads();
-    // CTA 0 exchanges the arrival signals with the peers and publishes the outcome in a local
-    // word; the other CTAs (a few, all resident at once) wait for that word.
-    if (blockIdx.x == 0) {
-        if ((int)threadIdx.x < d.world && (int)threadIdx.x != d.rank) {
-            const int p = threadIdx.x;
-            __threadfence_system();
-            st_release_sys(d.flags[p] + d.rank, e);  // "my partial sums of exchange e are in your inbox"
-            const uint32_t *mine = d.flags[d.rank] + p;
-            bool ok = false;
-            unsigned long long t0, now;
-            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
-            for (int spin = 0;; ++spin) {
-                // the count only grows; a peer that is ahead has already passed e
-                if ((int32_t)(ld_acquire_sys(mine) - e) >= 0) { ok = true; break; }
-                if ((spin & 63) == 63) {
-                    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-                    if (now - t0 > 2000000000ull) break;  // two seconds
-                }
-                __nanosleep(20);
-            }
-            if (!ok) failed = 1;
-        }
-        __syncthreads();
-        if (threadIdx.x == 0 && !failed)
-            asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(d.ready), "r"(e) : "memory");
-    } else {
-        if (threadIdx.x == 0) {
-            bool ok = false;
-            unsigned long long t0, now;
-            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
-            for (int spin = 0;; ++spin) {
-                uint32_t v;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(d.ready) : "memory");
-                if ((int32_t)(v - e) >= 0) { ok = true; break; }
-                if ((spin & 63) == 63) {
-                    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-                    if (now - t0 > 3000000000ull) break;  // CTA 0's own limit plus a margin
-                }
-                __nanosleep(20);
-            }
-            if (!ok) failed = 1;
-        }
-        __syncthreads();
-    }
-    if (failed) {
-        if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
-        return;
-    }
-    const float *box = d.inbox[d.rank] + (size_t)(e & 1u) * d.world * d.max_elems;
+    const unsigned long long *box = d.inbox[d.rank] + (size_t)(e & 1u) * d.world * d.max_elems;
     const size_t nvec = count >> 3;  // 8 elements per thread and pass
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
         float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int r = 0; r < d.world; ++r) {
-            const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)r * d.max_elems) + 2 * i);
-            const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(box + (size_t)r * d.max_elems) + 2 * i + 1);
-            sum[0] += p0.x; sum[1] += p0.y; sum[2] += p0.z; sum[3] += p0.w;
-            sum[4] += p1.x; sum[5] += p1.y; sum[6] += p1.z; sum[7] += p1.w;
+            float pv[8];
+            if (!tp_ll_wait8(box + (size_t)r * d.max_elems + 8 * i, e, d.wait_limit_ns, pv)) {
+                failed = 1;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pv[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] += pv[j];
         }
         const uint4 xv = reinterpret_cast<const uint4 *>(x)[i];
         uint32_t w[4] = {xv.x, xv.y, xv.z, xv.w};
@@ -172,15 +122,50 @@ tp_peer_reduce_add_kernel(__nv_bfloat16 *x, size_t count, const ab2_tp_peer_desc
     if (blockIdx.x == 0)  // a tail of fewer than 8 elements
         for (size_t i = (nvec << 3) + threadIdx.x; i < count; i += blockDim.x) {
             float sum = 0.f;
-            for (int r = 0; r < d.world; ++r) sum += __ldcg(box + (size_t)r * d.max_elems + i);
+            for (int r = 0; r < d.world; ++r) {
+                const unsigned long long *p = box + (size_t)r * d.max_elems + i;
+                unsigned long long w = 0, t0 = 0;
+                bool ok = false;
+                for (int spin = 0;; ++spin) {
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(w) : "l"(p) : "memory");
+                    if ((uint32_t)(w >> 32) == e) { ok = true; break; }
+                    if ((spin & 15) == 15) {
+                        const unsigned long long now = tp_wall_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > d.wait_limit_ns) break;
+                    }
+                }
+                if (!ok) failed = 1;
+                sum += ok ? __uint_as_float((uint32_t)w) : 0.f;
+            }
             x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) + __bfloat162float(__float2bfloat16_rn(sum)));
         }
     __syncthreads();
+    if (failed) {
+        // a peer's sums did not arrive within the limit (x holds what did arrive): record it; the
+        // exchange count stays, ab2_tp_peer_reset puts the ranks back in step
+        if (threadIdx.x == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+        return;
+    }
     // every CTA has read the exchange count and its share of the inbox: the last one closes the exchange
     if (threadIdx.x == 0 && atomicAdd(d.done, 1u) == gridDim.x - 1) {
         *d.done = 0;
         __threadfence();
         *d.epoch = e;
+    }
+}
+
+// This rank's partial sums of the current exchange into every rank's inbox.
+__global__ void __launch_bounds__(256)
+tp_peer_deposit_kernel(const float *partial, size_t count, const ab2_tp_peer_desc *desc) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const ab2_tp_peer_desc d = *desc;
+    const uint32_t e = *d.epoch + 1;
+    const size_t off = ((size_t)(e & 1u) * d.world + d.rank) * d.max_elems;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned long long w = tp_ll_pack(partial[i], e);
+        for (int p = 0; p < d.world; ++p) tp_ll_store(d.inbox[p] + off + i, w);
     }
 }
 
@@ -203,14 +188,25 @@ int tp_peer_reduce_add(ab2_tp *tp, void *x_bf16, size_t count, cudaStream_t s) {
     return AB2_OK;
 }
 
+int tp_peer_deposit(ab2_tp *tp, const float *partial_f32, size_t count, cudaStream_t s) {
+    AB2_REQUIRE(tp_peer_ready(tp, count), AB2_ERR_BAD_ARG, "the peer exchange is not attached or %zu elements exceed it", count);
+    const unsigned ctas = (unsigned)std::max<size_t>(1, std::min<size_t>(64, (count + 255) / 256));
+    cudaError_t e = launch_kernel(tp_peer_deposit_kernel, dim3(ctas), dim3(256), 0, s, partial_f32, count,
+                                  (const ab2_tp_peer_desc *)tp->desc_dev);
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "peer deposit launch failed: %s", cudaGetErrorString(e));
+    return AB2_OK;
+}
+
 int tp_all_reduce(ab2_tp *tp, void *buf, size_t count, ab2_dtype dtype, cudaStream_t s) {
     if (!tp || tp->world == 1) return AB2_OK;
+    AB2_REQUIRE(tp->comm != nullptr, AB2_ERR_UNSUPPORTED, "this tensor-parallel context was created without a communicator");
     AB2_NCCL(g_nccl.AllReduce(buf, buf, count, nccl_type(dtype), ncclSum, (ncclComm_t)tp->comm, s));
     return AB2_OK;
 }
 
 int tp_all_gather(ab2_tp *tp, const void *send, void *recv, size_t count, ab2_dtype dtype, cudaStream_t s) {
     AB2_REQUIRE(tp != nullptr, AB2_ERR_BAD_ARG, "null tensor-parallel context");
+    AB2_REQUIRE(tp->comm != nullptr, AB2_ERR_UNSUPPORTED, "this tensor-parallel context was created without a communicator");
     AB2_NCCL(g_nccl.AllGather(send, recv, count, nccl_type(dtype), (ncclComm_t)tp->comm, s));
     return AB2_OK;
 }
@@ -235,8 +231,8 @@ AB2_API int ab2_tp_create(ab2_tp **out, int rank, int world, const void *id128) 
     tp->rank = rank; tp->world = world; tp->comm = nullptr;
     tp->local_block = nullptr; tp->desc_dev = nullptr; tp->max_elems = 0; tp->attached = false;
     for (int i = 0; i < AB2_TP_MAX_WORLD; ++i) tp->peer_block[i] = nullptr;
-    if (world > 1) {
-        AB2_REQUIRE(id128 != nullptr, AB2_ERR_BAD_ARG, "a unique id is needed for more than one rank");
+    tp->wait_limit_ns = 2000000000ull;
+    if (world > 1 && id128 != nullptr) {
         int rc = load_nccl();
         if (rc != AB2_OK) { delete tp; return rc; }
         ncclUniqueId id;
@@ -269,52 +265,105 @@ AB2_API int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype
     return tp_all_reduce(tp, buf_dev, count, dtype, (cudaStream_t)stream);
 }
 
-// Layout of a rank's block: inbox [2][world][max_elems] f32, then flags [world] u32, the epoch, done and ready words.
-static size_t peer_block_bytes(int world, size_t max_elems) {
-    return 2 * (size_t)world * max_elems * sizeof(float) + ((size_t)world + 3) * sizeof(uint32_t) + 256;
+// Layout of a rank's block: inbox [2][world][max_elems] 8-byte words, then the epoch and done words.
+static size_t peer_inbox_words(int world, size_t max_elems) { return 2 * (size_t)world * max_elems; }
+static size_t peer_block_bytes(int world, size_t max_elems) { return peer_inbox_words(world, max_elems) * 8 + 256; }
+
+static int peer_fill_desc(ab2_tp *tp, void *const *blocks) {
+    ab2_tp_peer_desc d;
+    memset(&d, 0, sizeof(d));
+    for (int p = 0; p < tp->world; ++p) d.inbox[p] = (unsigned long long *)blocks[p];
+    uint32_t *words = (uint32_t *)((unsigned long long *)tp->local_block + peer_inbox_words(tp->world, tp->max_elems));
+    d.epoch = words;
+    d.done = words + 1;
+    d.rank = tp->rank; d.world = tp->world; d.max_elems = tp->max_elems;
+    d.wait_limit_ns = tp->wait_limit_ns;
+    if (!tp->desc_dev) AB2_CUDA(cudaMalloc((void **)&tp->desc_dev, sizeof(d)));
+    AB2_CUDA(cudaMemcpy(tp->desc_dev, &d, sizeof(d), cudaMemcpyHostToDevice));
+    tp->attached = true;
+    return AB2_OK;
 }
 
 AB2_API int ab2_tp_peer_export(ab2_tp *tp, size_t max_elems, void *handle64_host) {
-    AB2_REQUIRE(tp && handle64_host, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(tp != nullptr, AB2_ERR_BAD_ARG, "null argument");
     AB2_REQUIRE(tp->world > 1 && tp->world <= AB2_TP_MAX_WORLD, AB2_ERR_UNSUPPORTED,
                 "the peer exchange serves 2..%d ranks, got %d", AB2_TP_MAX_WORLD, tp->world);
-    AB2_REQUIRE(max_elems > 0 && max_elems % 4 == 0, AB2_ERR_BAD_SHAPE, "max_elems must be a positive multiple of 4");
+    AB2_REQUIRE(max_elems > 0 && max_elems % 8 == 0, AB2_ERR_BAD_SHAPE, "max_elems must be a positive multiple of 8");
     AB2_REQUIRE(tp->local_block == nullptr, AB2_ERR_BAD_ARG, "the peer exchange was exported already");
     const size_t bytes = peer_block_bytes(tp->world, max_elems);
     AB2_CUDA(cudaMalloc(&tp->local_block, bytes));
     AB2_CUDA(cudaMemset(tp->local_block, 0, bytes));
     AB2_CUDA(cudaDeviceSynchronize());
     tp->max_elems = max_elems;
-    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle is 64 bytes");
-    cudaIpcMemHandle_t h;
-    AB2_CUDA(cudaIpcGetMemHandle(&h, tp->local_block));
-    memcpy(handle64_host, &h, 64);
+    if (handle64_host) {  // a single-process caller that attaches by pointer needs no IPC handle
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle is 64 bytes");
+        cudaIpcMemHandle_t h;
+        AB2_CUDA(cudaIpcGetMemHandle(&h, tp->local_block));
+        memcpy(handle64_host, &h, 64);
+    }
+    return AB2_OK;
+}
+
+AB2_API int ab2_tp_peer_block(ab2_tp *tp, void **block_dev, size_t *bytes) {
+    AB2_REQUIRE(tp && block_dev, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(tp->local_block != nullptr, AB2_ERR_BAD_ARG, "export the local block first");
+    *block_dev = tp->local_block;
+    if (bytes) *bytes = peer_block_bytes(tp->world, tp->max_elems);
     return AB2_OK;
 }
 
 AB2_API int ab2_tp_peer_attach(ab2_tp *tp, const void *handles_host) {
     AB2_REQUIRE(tp && handles_host, AB2_ERR_BAD_ARG, "null argument");
     AB2_REQUIRE(tp->local_block != nullptr && !tp->attached, AB2_ERR_BAD_ARG, "export the local block first (once)");
-    ab2_tp_peer_desc d;
-    memset(&d, 0, sizeof(d));
-    const size_t inbox_floats = 2 * (size_t)tp->world * tp->max_elems;
+    void *blocks[AB2_TP_MAX_WORLD] = {nullptr};
     for (int p = 0; p < tp->world; ++p) {
-        void *base = tp->local_block;
+        blocks[p] = tp->local_block;
         if (p != tp->rank) {
             cudaIpcMemHandle_t h;
             memcpy(&h, (const char *)handles_host + (size_t)p * 64, 64);
             AB2_CUDA(cudaIpcOpenMemHandle(&tp->peer_block[p], h, cudaIpcMemLazyEnablePeerAccess));
-            base = tp->peer_block[p];
+            blocks[p] = tp->peer_block[p];
         }
-        d.inbox[p] = (float *)base;
-        d.flags[p] = (uint32_t *)((float *)base + inbox_floats);
     }
-    d.epoch = d.flags[tp->rank] + tp->world;
-    d.done = d.epoch + 1;
-    d.ready = d.epoch + 2;
-    d.rank = tp->rank; d.world = tp->world; d.max_elems = tp->max_elems;
-    AB2_CUDA(cudaMalloc((void **)&tp->desc_dev, sizeof(d)));
-    AB2_CUDA(cudaMemcpy(tp->desc_dev, &d, sizeof(d), cudaMemcpyHostToDevice));
-    tp->attached = true;
+    return peer_fill_desc(tp, blocks);
+}
+
+AB2_API int ab2_tp_peer_attach_ptrs(ab2_tp *tp, void *const *blocks_dev) {
+    AB2_REQUIRE(tp && blocks_dev, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(tp->local_block != nullptr && !tp->attached, AB2_ERR_BAD_ARG, "export the local block first (once)");
+    void *blocks[AB2_TP_MAX_WORLD] = {nullptr};
+    for (int p = 0; p < tp->world; ++p) {
+        blocks[p] = p == tp->rank ? tp->local_block : blocks_dev[p];
+        AB2_REQUIRE(blocks[p] != nullptr && ((uintptr_t)blocks[p] & 15) == 0, AB2_ERR_BAD_ARG, "block of rank %d is null or misaligned", p);
+    }
+    return peer_fill_desc(tp, blocks);
+}
+
+AB2_API int ab2_tp_set_wait_limit_ns(ab2_tp *tp, unsigned long long limit_ns) {
+    AB2_REQUIRE(tp != nullptr && limit_ns > 0, AB2_ERR_BAD_ARG, "null context or zero limit");
+    tp->wait_limit_ns = limit_ns;
+    if (tp->desc_dev) {
+        AB2_CUDA(cudaDeviceSynchronize());
+        AB2_CUDA(cudaMemcpy((char *)tp->desc_dev + offsetof(ab2_tp_peer_desc, wait_limit_ns), &limit_ns, sizeof(limit_ns),
+                            cudaMemcpyHostToDevice));
+    }
     return AB2_OK;
+}
+
+AB2_API int ab2_tp_peer_reset(ab2_tp *tp) {
+    AB2_REQUIRE(tp != nullptr && tp->local_block != nullptr, AB2_ERR_BAD_ARG, "the peer exchange was not exported");
+    AB2_CUDA(cudaDeviceSynchronize());
+    AB2_CUDA(cudaMemset(tp->local_block, 0, peer_block_bytes(tp->world, tp->max_elems)));
+    AB2_CUDA(cudaDeviceSynchronize());
+    return AB2_OK;
+}
+
+AB2_API int ab2_tp_peer_deposit(ab2_tp *tp, const float *partial_dev, size_t count, ab2_stream stream) {
+    AB2_REQUIRE(tp && partial_dev, AB2_ERR_BAD_ARG, "null argument");
+    return tp_peer_deposit(tp, partial_dev, count, (cudaStream_t)stream);
+}
+
+AB2_API int ab2_tp_peer_reduce_add(ab2_tp *tp, void *x_bf16_dev, size_t count, ab2_stream stream) {
+    AB2_REQUIRE(tp && x_bf16_dev, AB2_ERR_BAD_ARG, "null argument");
+    return tp_peer_reduce_add(tp, x_bf16_dev, count, (cudaStream_t)stream);
 }

@@ -109,6 +109,38 @@ class TensorParallel:
         check(lib.ab2_tp_peer_attach(self._h, C.create_string_buffer(b"".join(handles), 64 * self.world)))
         dist.barrier()
 
+    # -- the peer exchange as a stand-alone one-shot all-reduce --------------------
+    def export_block(self, max_elems: int):
+        """Allocates this rank's inbox without an IPC handle and returns (device pointer, bytes)."""
+        check(lib.ab2_tp_peer_export(self._h, max_elems, None))
+        ptr, n = C.c_void_p(), C.c_size_t()
+        check(lib.ab2_tp_peer_block(self._h, C.byref(ptr), C.byref(n)))
+        return ptr.value, n.value
+
+    def attach_blocks(self, block_ptrs) -> None:
+        """Attaches by device pointers of every rank's block as this process sees them."""
+        arr = (C.c_void_p * self.world)(*[int(b) if b else None for b in block_ptrs])
+        check(lib.ab2_tp_peer_attach_ptrs(self._h, arr))
+
+    def set_wait_limit_ns(self, ns: int) -> None:
+        check(lib.ab2_tp_set_wait_limit_ns(self._h, int(ns)))
+
+    def peer_reset(self) -> None:
+        check(lib.ab2_tp_peer_reset(self._h))
+
+    def peer_deposit(self, partial: torch.Tensor) -> None:
+        from .qlinear import stream_ptr
+        if partial.dtype != torch.float32 or not partial.is_contiguous():
+            raise ValueError("partial sums must be a contiguous float32 tensor")
+        check(lib.ab2_tp_peer_deposit(self._h, partial.data_ptr(), partial.numel(), stream_ptr()))
+
+    def peer_reduce_add(self, x: torch.Tensor) -> torch.Tensor:
+        from .qlinear import stream_ptr
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("the residual stream must be a contiguous bfloat16 tensor")
+        check(lib.ab2_tp_peer_reduce_add(self._h, x.data_ptr(), x.numel(), stream_ptr()))
+        return x
+
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         from .qlinear import dtype_code, stream_ptr
         check(lib.ab2_tp_all_reduce(self._h, t.data_ptr(), t.numel(), dtype_code(t.dtype), stream_ptr()))

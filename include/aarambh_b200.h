@@ -294,25 +294,50 @@ int ab2_model_rope_tables(const ab2_model *m, const float **cos_dev, const float
  * After wo and w_down the partial sums are all-reduced; the logits shards are
  * all-gathered.  ab2_model_set_tp must precede the lm_head and ab2_model_finalize. */
 int ab2_tp_unique_id(void *id128_host);
+/* id128_host may be NULL for world > 1: the context then has no NCCL communicator and serves
+ * the peer exchange only (ab2_tp_all_reduce and a vocabulary-parallel head need the communicator). */
 int ab2_tp_create(ab2_tp **out, int rank, int world, const void *id128_host);
 int ab2_tp_destroy(ab2_tp *tp);
 /* In-place sum over ranks of `count` elements (NCCL all-reduce). */
 int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype dtype, ab2_stream stream);
-/* One-shot exchange of the decoder's f32 partial sums over NVLink peer memory
- * instead of NCCL (no counterpart in the reference, whose only collective is the
- * NCCL all-reduce above).  Every rank calls ab2_tp_peer_export (allocates its
- * inbox for up to max_elems sums per rank and writes a 64-byte CUDA IPC handle
- * to handle64_host), the caller gathers the handles of all ranks in rank order
- * (world x 64 bytes, the same channel that carried the unique id), and every
- * rank calls ab2_tp_peer_attach with them.  From then on a decoder whose step has
- * at most 16 tokens and tokens x d_model <= max_elems lets the row-parallel
- * projections store their sums into every rank's inbox and meets the other
- * ranks in one small kernel per exchange (bounded wait; AB2_ERR_TIMEOUT in the
- * device status word when a peer does not arrive).  The ranks must be processes
- * on GPUs of one box with peer access; every rank must run the same sequence of
- * steps.  Attach before the first step is captured. */
+/* One-shot exchange of f32 partial sums over NVLink peer memory instead of NCCL (no counterpart
+ * in the reference, whose only collective is the NCCL all-reduce above).  Every rank owns an
+ * inbox; a partial sum travels as ONE 8-byte word {f32 sum, u32 exchange number} stored straight
+ * into every rank's inbox, and a reader that finds the exchange number it waits for has the sum
+ * that came with it: no flag, no fence, no signal round trip.  Inboxes are double-buffered by the
+ * parity of a per-rank exchange count kept in device memory.
+ *
+ * Set-up: every rank calls ab2_tp_peer_export (allocates its inbox for up to max_elems sums per
+ * rank, a multiple of 8, and writes a 64-byte CUDA IPC handle to handle64_host, which may be
+ * NULL), the caller gathers the handles of all ranks in rank order (world x 64 bytes, the same
+ * channel that carried the unique id), and every rank calls ab2_tp_peer_attach with them.  A
+ * single process that drives several GPUs (or a test that plays a peer itself) instead reads
+ * each context's block with ab2_tp_peer_block and calls ab2_tp_peer_attach_ptrs with the
+ * device pointers of all ranks' blocks as seen from this rank (peer access enabled by the
+ * caller); such contexts may be created with a NULL unique id (no NCCL communicator).
+ *
+ * Use: a decoder whose step has at most 16 tokens and tokens x d_model <= max_elems lets its
+ * row-parallel projections store their sums into every rank's inbox and consumes them in the
+ * next projection's prologue.  The same exchange is callable directly: ab2_tp_peer_deposit
+ * stores this rank's `count` partial sums with every rank, ab2_tp_peer_reduce_add adds the sum
+ * over ranks (in rank order, rounded to bf16 once) to x_bf16_dev; every rank must call the pair
+ * the same number of times with the same count.
+ *
+ * A reader waits at most the wait limit (default two seconds, ab2_tp_set_wait_limit_ns) for a
+ * peer's words; when it runs out the kernel records AB2_ERR_TIMEOUT in the device status word
+ * and returns, leaving the exchange count as it was.  Callers that can lose a peer should read
+ * ab2_device_status every few steps; after a time-out the ranks' counts may differ, and every
+ * rank calls ab2_tp_peer_reset (between two host-side barriers of the caller's) to clear its
+ * inbox and count before the exchange is used again.  The ranks must be on GPUs of one box with
+ * peer access; attach before the first step is captured in a graph. */
 int ab2_tp_peer_export(ab2_tp *tp, size_t max_elems, void *handle64_host);
 int ab2_tp_peer_attach(ab2_tp *tp, const void *handles_host);
+int ab2_tp_peer_block(ab2_tp *tp, void **block_dev, size_t *bytes);
+int ab2_tp_peer_attach_ptrs(ab2_tp *tp, void *const *blocks_dev);
+int ab2_tp_set_wait_limit_ns(ab2_tp *tp, unsigned long long limit_ns);
+int ab2_tp_peer_reset(ab2_tp *tp);
+int ab2_tp_peer_deposit(ab2_tp *tp, const float *partial_dev, size_t count, ab2_stream stream);
+int ab2_tp_peer_reduce_add(ab2_tp *tp, void *x_bf16_dev, size_t count, ab2_stream stream);
 int ab2_model_set_tp(ab2_model *m, ab2_tp *tp);
 /* AarambhModel::forward_with_cache (model.rs:508-587; nrows = 1, S = prompt
  * length) and forward_decode_batch (model.rs:590-641; S = 1): ids_dev
