@@ -307,6 +307,14 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
         }
         return AB2_OK;
     }
+    if (S > 1) {
+        // prefill chunk over an INT8 cache: the tensor-core causal kernel (attention_mma.cu)
+        static const bool scalar_prefill = getenv("AB2_SCALAR_PREFILL_ATTN") != nullptr;  // measurement switch
+        if (!scalar_prefill) {
+            int rc = attention_prefill_mma_device(kv, layer, q, out, S, pending, row0, nrows, scale, dtype, st, s);
+            if (rc != AB2_ERR_UNSUPPORTED) return rc;
+        }
+    }
     if (S == 1) nsplit = decode_split_count(kv, nrows, max_len, kv->max_splits, false);
     a.nsplit = nsplit;
     dim3 grid(nsplit, kv->kvh, nrows * S);

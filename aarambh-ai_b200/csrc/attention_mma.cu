@@ -264,6 +264,228 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(MmaAttnArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Causal attention of S new queries per sequence over the INT8 cache (prefill
+// chunks, speculative verification): GroupedQueryAttention::forward at S > 1
+// (crates/aarambh-studio-nn/src/attention.rs:170-226) with the causal cut of
+// dispatch.rs:145-160 (query i sees keys up to kv_len - q_len + i).
+//
+// Same tensor-core arithmetic as the decode kernel above with the roles of the
+// MMA rows changed: a warp owns 16 consecutive queries of ONE query head (the A
+// rows of Q.K^T), walks the keys 16 at a time up to the causal limit of its last
+// query, keeps the online softmax of its 16 rows in registers and accumulates
+// O^T = V^T . P^T for queries 0-7 and 8-15 with the same V^T fragments.  The warps
+// of a CTA are the query heads of one KV head on the same 16 queries, so the K
+// rows and V blocks they fetch are the same bytes (cache hits after the first).
+// No cross-warp merge and no context split: every (head, query tile) is a warp.
+// ---------------------------------------------------------------------------
+struct PrefillAttnArgs {
+    KvView kv;
+    const void *q;
+    void *out;
+    AttnStrides st;
+    int S, pending, row0, rep, dtype;
+    float scale;
+};
+
+__global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillAttnArgs a) {
+    constexpr int HD = 128;
+    __shared__ alignas(128) uint8_t vst[4][2][16 * HD];  // per warp, double-buffered V block (swizzled 16-byte chunks)
+    pdl_wait();
+    pdl_launch_dependents();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    if (warp >= a.rep) return;  // no barrier below: a spare warp may leave
+    const int qt = blockIdx.x, kvhead = blockIdx.y, rrow = blockIdx.z, row = kv_row(a.kv, a.row0, rrow);
+    const int head = kvhead * a.rep + warp;
+    const int q_lo = qt * 16;
+    // keys visible to query i: [0, first + i]; first = cached + appended - S
+    const int first = a.kv.lens[row] + a.pending - a.S;
+    const int kmax = first + min(a.S, q_lo + 16);  // keys the tile's last query sees
+    const size_t head_base = ((size_t)row * a.kv.kvh + kvhead) * a.kv.cap;
+    const int8_t *kbase = (const int8_t *)a.kv.k + head_base * HD;
+    const int8_t *vbase = (const int8_t *)a.kv.v + head_base * HD;
+    const float *ksc = a.kv.ks + head_base, *vsc = a.kv.vs + head_base;
+
+    // ---- Q fragments: rows g and g + 8 = queries q_lo + g, q_lo + g + 8; k-step s covers
+    // d = c*32 + 4s + {0,1} (a0 / a1) and {2,3} (a2 / a3)
+    uint32_t qa0[8], qa1[8], qa2[8], qa3[8];
+    {
+        const int qa = q_lo + g, qb = q_lo + g + 8;
+        const size_t ba = (size_t)((long long)rrow * a.st.q_b + (long long)qa * a.st.q_s + (long long)head * a.st.q_h) + c * 32;
+        const size_t bb = (size_t)((long long)rrow * a.st.q_b + (long long)qb * a.st.q_s + (long long)head * a.st.q_h) + c * 32;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (qa < a.S)
+                for (int j = 0; j < 4; ++j) v[j] = q_as_f32(a.q, a.dtype, ba + 4 * s + j);
+            if (qb < a.S)
+                for (int j = 0; j < 4; ++j) v[4 + j] = q_as_f32(a.q, a.dtype, bb + 4 * s + j);
+            qa0[s] = pack_f16(v[0], v[1]); qa2[s] = pack_f16(v[2], v[3]);
+            qa1[s] = pack_f16(v[4], v[5]); qa3[s] = pack_f16(v[6], v[7]);
+        }
+    }
+    const int end_a = first + q_lo + g + 1, end_b = end_a + 8;  // exclusive key limits of this thread's two rows
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[8][2][4];  // [d chunk][queries 0-7 / 8-15][fragment]: rows d, d + 1; columns queries 2c, 2c + 1
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[i][h2][j] = 0.f;
+
+    auto stage_v = [&](int base, int buf) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = lane + 32 * i, tok = idx >> 3, ch = idx & 7;
+            const int src_tok = min(base + tok, kmax - 1);
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&vst[warp][buf][tok * HD + ((ch ^ (tok & 7)) << 4)]);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(vbase + (size_t)src_tok * HD + ch * 16));
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    auto load_k = [&](int base, uint4 (&kr)[4], float (&sc)[8]) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int tok = min(base + nt * 8 + g, kmax - 1);
+            const uint4 *p = reinterpret_cast<const uint4 *>(kbase + (size_t)tok * HD + c * 32);
+            kr[2 * nt] = p[0];
+            kr[2 * nt + 1] = p[1];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = min(base + nt * 8 + 2 * c + e, kmax - 1);
+                sc[nt * 2 + e] = ksc[tok];
+                sc[4 + nt * 2 + e] = vsc[tok];
+            }
+    };
+
+    int buf = 0;
+    uint4 kr[4];
+    float sc[8];
+    if (kmax > 0) { stage_v(0, 0); load_k(0, kr, sc); }
+    for (int base = 0; base < kmax; base += 16) {
+        uint4 kr_n[4];
+        float sc_n[8];
+        const int nxt = base + 16;
+        if (nxt < kmax) { stage_v(nxt, buf ^ 1); load_k(nxt, kr_n, sc_n); }
+
+        // ---- S = Q.K^T for two 8-token tiles (rows g: fragments 0,1; rows g + 8: fragments 2,3)
+        float s_frag[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s_frag[nt][j] = 0.f;
+            const uint32_t w[8] = {kr[2 * nt].x ^ 0x80808080u, kr[2 * nt].y ^ 0x80808080u, kr[2 * nt].z ^ 0x80808080u,
+                                   kr[2 * nt].w ^ 0x80808080u, kr[2 * nt + 1].x ^ 0x80808080u, kr[2 * nt + 1].y ^ 0x80808080u,
+                                   kr[2 * nt + 1].z ^ 0x80808080u, kr[2 * nt + 1].w ^ 0x80808080u};
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                mma_f16_16816(s_frag[nt], qa0[s], qa1[s], qa2[s], qa3[s], i8_pair_f16<0, 1>(w[s]), i8_pair_f16<2, 3>(w[s]));
+        }
+        // ---- online softmax of rows g and g + 8 over the 16 tokens (causal: token < row limit)
+        float pv[2][4], corr[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const int lim = h2 ? end_b : end_a;
+            float sv[4], bm = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const bool valid = base + nt * 8 + 2 * c + e < lim;
+                    sv[nt * 2 + e] = valid ? s_frag[nt][2 * h2 + e] * sc[nt * 2 + e] * a.scale : -INFINITY;
+                    bm = fmaxf(bm, sv[nt * 2 + e]);
+                }
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+            const float m_new = fmaxf(m_run[h2], bm);
+            // a row with no visible key yet keeps m = -inf; exp(-inf - -inf) must not become NaN
+            corr[h2] = m_new == -INFINITY ? 1.f : expf(m_run[h2] - m_new);
+            float psum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                pv[h2][i] = m_new == -INFINITY ? 0.f : expf(sv[i] - m_new);
+                psum += pv[h2][i];
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            l_run[h2] = l_run[h2] * corr[h2] + psum;
+            m_run[h2] = m_new;
+        }
+        // P^T fragments (B operand of P.V) for queries 0-7 and 8-15, times the V scale of their token
+        uint32_t pb0[2], pb1[2];
+        float c0[2], c1[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            pb0[h2] = pack_f16(pv[h2][0] * sc[4], pv[h2][1] * sc[5]);
+            pb1[h2] = pack_f16(pv[h2][2] * sc[6], pv[h2][3] * sc[7]);
+            // rescale factors of the queries this thread's output columns belong to (rows 2c, 2c + 1 of the half)
+            c0[h2] = __shfl_sync(0xffffffffu, corr[h2], (2 * c) * 4);
+            c1[h2] = __shfl_sync(0xffffffffu, corr[h2], (2 * c + 1) * 4);
+        }
+
+        // ---- O^T += V^T . P^T  (V block staged in shared memory)
+        if (nxt < kmax) asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncwarp();
+        const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(&vst[warp][buf][0]);
+        const int lm = lane >> 3, lr = lane & 7, ltok = (lm & 1) * 8 + lr;
+#pragma unroll
+        for (int dp = 0; dp < 4; ++dp) {
+            const int ch = 2 * dp + (lm >> 1);
+            const uint32_t addr = vs_base + ltok * HD + ((ch ^ (ltok & 7)) << 4);
+            uint32_t r0, r1, r2, r3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                         : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+            r0 ^= 0x80808080u; r1 ^= 0x80808080u; r2 ^= 0x80808080u; r3 ^= 0x80808080u;
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+                const uint32_t lo = hc ? r2 : r0, hi = hc ? r3 : r1;
+                const uint32_t va0 = i8_pair_f16<0, 2>(lo), va1 = i8_pair_f16<1, 3>(lo), va2 = i8_pair_f16<0, 2>(hi), va3 = i8_pair_f16<1, 3>(hi);
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    float (&acc)[4] = o[2 * dp + hc][h2];
+                    acc[0] *= c0[h2]; acc[1] *= c1[h2]; acc[2] *= c0[h2]; acc[3] *= c1[h2];
+                    mma_f16_16816(acc, va0, va1, va2, va3, pb0[h2], pb1[h2]);
+                }
+            }
+        }
+        __syncwarp();
+        if (nxt < kmax) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) kr[i] = kr_n[i];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sc[i] = sc_n[i];
+        }
+        buf ^= 1;
+    }
+
+    // ---- normalise and store: this thread holds dims (d, d + 1), d = ch*16 + 2g, of queries 2c, 2c + 1 of each half
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        const float l0 = __shfl_sync(0xffffffffu, l_run[h2], (2 * c) * 4), l1 = __shfl_sync(0xffffffffu, l_run[h2], (2 * c + 1) * 4);
+        const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int qi = q_lo + 8 * h2 + 2 * c + e;
+            if (qi >= a.S) continue;
+            const size_t ob = (size_t)((long long)rrow * a.st.o_b + (long long)qi * a.st.o_s + (long long)head * a.st.o_h);
+            const float inv = e ? i1 : i0;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                const int d = ch * 16 + 2 * g;
+                st_out(a.out, a.dtype, ob + d, o[ch][h2][e] * inv);
+                st_out(a.out, a.dtype, ob + d + 1, o[ch][h2][2 + e] * inv);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // Returns AB2_ERR_UNSUPPORTED when the cache or head layout is not the one this
@@ -279,6 +501,21 @@ int attention_decode_mma_device(const ab2_kv *kv, int layer, const void *q, void
     a.pending = pending; a.q_stride = q_stride;
     cudaError_t e = launch_kernel(attn_decode_mma_kernel, dim3(nsplit, kv->kvh, nrows), dim3(128), 0, s, a);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "decode attention launch failed: %s", cudaGetErrorString(e));
+    return AB2_OK;
+}
+
+// S > 1 queries per row over an INT8 cache, head_dim 128, 1..4 query heads per KV head: the
+// tensor-core causal kernel.  AB2_ERR_UNSUPPORTED otherwise (the caller keeps the general kernel).
+int attention_prefill_mma_device(const ab2_kv *kv, int layer, const void *q, void *out, int S, int pending, int row0,
+                                 int nrows, float scale, ab2_dtype dtype, AttnStrides st, cudaStream_t s) {
+    const int rep = kv->h / kv->kvh;
+    if (kv->dtype != AB2_KV_INT8 || kv->hd != 128 || rep > 4 || S < 2) return AB2_ERR_UNSUPPORTED;
+    PrefillAttnArgs a;
+    a.kv = kv_view(kv, layer);
+    a.q = q; a.out = out; a.st = st; a.S = S; a.pending = pending; a.row0 = row0; a.rep = rep;
+    a.dtype = (int)dtype; a.scale = scale;
+    cudaError_t e = launch_kernel(attn_prefill_mma_kernel, dim3((S + 15) / 16, kv->kvh, nrows), dim3(128), 0, s, a);
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "prefill attention launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 

@@ -73,6 +73,10 @@ int attention_cached_device(const ab2_kv *kv, int layer, const void *q, void *ou
 int attention_decode_mma_device(const ab2_kv *kv, int layer, const void *q, void *out, int row0, int nrows,
                                 float scale, ab2_dtype dtype, int nsplit, float *part_acc, float *part_ml,
                                 int pending, long long q_stride, cudaStream_t s);
+// Causal attention of S > 1 new queries per row over an INT8 cache (head_dim 128, up to 4 query
+// heads per KV head) on the tensor cores; AB2_ERR_UNSUPPORTED for other layouts.
+int attention_prefill_mma_device(const ab2_kv *kv, int layer, const void *q, void *out, int S, int pending, int row0,
+                                 int nrows, float scale, ab2_dtype dtype, AttnStrides st, cudaStream_t s);
 int attention_decode_fused_device(ab2_kv *kv, int layer, const void *qkv, long long stride, void *out,
                                   int row0, int nrows, float scale, ab2_dtype dtype, const float *cos_t,
                                   const float *sin_t, const int *rope_pos, int len_hint, cudaStream_t s);

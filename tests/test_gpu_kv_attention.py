@@ -202,3 +202,30 @@ def test_attention_errors():
         p.dispatch.attention_forward_causal(torch.zeros(1, 2, 3, 16, device="cuda"),
                                             torch.zeros(2, 2, 3, 16, device="cuda"),
                                             torch.zeros(2, 2, 3, 16, device="cuda"), 1.0)
+
+
+@pytest.mark.parametrize("lens,S,h,kvh", [([512], 512, 32, 8), ([82, 45], 45, 8, 2), ([317, 600], 17, 4, 4),
+                                          ([2, 40], 2, 32, 8), ([1030], 129, 16, 8)])
+def test_prefill_attention_over_int8_cache_on_tensor_cores(lens, S, h, kvh):
+    """S > 1 queries per sequence over an INT8 cache, head_dim 128 (prefill chunks, speculative
+    verification): the tensor-core causal kernel against the oracle's causal attention over
+    exactly what the cache holds.  Covers the 512-token prompt of the decode benchmark at
+    32 / 8 heads, chunks that are not multiples of the 16-query tile, a cached prefix, ragged
+    rows and every heads-per-KV-head ratio the kernel serves (1, 2, 4)."""
+    rng = np.random.default_rng(34)
+    hd, B = 128, len(lens)
+    p = pkg()
+    cache = p.KVCache(max(lens), kvh, hd, h, batch=B, dtype="int8")
+    k = rng.standard_normal((B, max(lens), kvh, hd)).astype(np.float32)
+    v = rng.standard_normal((B, max(lens), kvh, hd)).astype(np.float32)
+    _fill(cache, k, v, lens)
+    q = orc.round_bf16(rng.standard_normal((B, S, h, hd)).astype(np.float32))
+    scale = 1.0 / math.sqrt(hd)
+    got = p.dispatch.attention_cached(cache, cuda(q, torch.bfloat16), scale).float().cpu().numpy()
+    assert p.device_status() == 0
+    for b, n in enumerate(lens):
+        kd, vd = [t.cpu().numpy() for t in cache.read(b)]          # [n, kvh, hd], dequantised
+        kr = np.repeat(kd[None], h // kvh, axis=2).transpose(0, 2, 1, 3)
+        vr = np.repeat(vd[None], h // kvh, axis=2).transpose(0, 2, 1, 3)
+        ref = orc.attention(q[b:b + 1].transpose(0, 2, 1, 3), kr, vr, scale, causal=True).transpose(0, 2, 1, 3)
+        assert rel_err(got[b], ref[0]) < 1e-2, (b, n)
