@@ -7,6 +7,8 @@ launch reads from HBM.
     python microbench.py gemv      [--m 1,4,16]      W4A16 dequant-GEMV (HBM GB/s)
     python microbench.py gemm      [--m 512,2048]    W4A16 tcgen05 GEMM (TFLOP/s)
     python microbench.py attention [--cases 8x16384] INT8-KV flash-decode (HBM GB/s)
+    python microbench.py prefill_attention [--cases 1x512] causal attention of a prompt over the INT8 cache
+    python microbench.py gemv|gemm --fmt int8             the same two for INT8 per-channel weights
     python microbench.py step      [--layers 2] [--ctx 512] one-token decoder step of a short
                                                    Large-shaped stack (a few hundred MB on the device: the
                                                    case to capture the step's kernels under a profiler)
@@ -185,6 +187,36 @@ def bench_attention(pkg, args):
         del cache
 
 
+def bench_prefill_attention(pkg, args):
+    """Causal attention of S new queries over an INT8 cache that ends with their own keys (32 / 8 heads of
+    128): the prefill kernel on its own, per layer of the Large config."""
+    h, kvh, hd = 32, 8, 128
+    for B, S in args.cases:
+        cache = pkg.KVCache(S, kvh, hd, h, batch=B, dtype="int8")
+        g = torch.Generator(device="cuda").manual_seed(3)
+        for b in range(B):
+            k = torch.randn((1, S, kvh, hd), generator=g, device="cuda", dtype=torch.bfloat16)
+            cache.update(k, k, row0=b)
+        q = torch.randn((B, S, h, hd), generator=g, device="cuda").to(torch.bfloat16)
+        scale = 1 / math.sqrt(hd)
+        for _ in range(3):
+            pkg.dispatch.attention_cached(cache, q, scale)
+        torch.cuda.synchronize()
+        if args.profile:
+            print("profiled case", B, S)
+            return
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            pkg.dispatch.attention_cached(cache, q, scale)
+        b_.record()
+        torch.cuda.synchronize()
+        t = a.elapsed_time(b_) * 1e-3 / 10
+        fl = B * 2.0 * 2.0 * h * hd * S * (S + 1) / 2
+        print(json.dumps({"kernel": "attn_prefill_mma_kernel", "B": B, "S": S, "us": round(t * 1e6, 1),
+                          "TFLOPs": round(fl / t / 1e12, 1)}), flush=True)
+
+
 def bench_step(pkg, args):
     """Decode steps of an n-layer stack with the Large block shapes (d 4096, 32 / 8 heads of 128, hidden 14336,
     vocab 32000; W4A16 g128, INT8 KV, bf16), context `ctx`.  Prints the step time; with --profile runs 4 steps."""
@@ -238,7 +270,7 @@ def bench_step(pkg, args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm", "attention", "step"])
+    ap.add_argument("what", choices=["gemv", "gemm", "attention", "prefill_attention", "step"])
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--m", default=None)
@@ -260,6 +292,9 @@ def main():
         bench_gemm(pkg, args)
     elif args.what == "step":
         bench_step(pkg, args)
+    elif args.what == "prefill_attention":
+        args.cases = [tuple(int(v) for v in c.split("x")) for c in (args.cases or "1x512,1x2048,4x512").split(",")]
+        bench_prefill_attention(pkg, args)
     else:
         default = "1x4096,1x16384,1x32768,8x4096,8x16384,8x32768,64x4096,64x16384,64x32768"
         args.cases = [tuple(int(v) for v in c.split("x")) for c in (args.cases or default).split(",")]
