@@ -105,32 +105,32 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(GemvArgs a, const T *
     int n = blockIdx.x * (blockDim.x >> 5) + warp;
     if (n >= a.N) return;
     const int words = a.K >> 3;
-  for (int m0 = 0; m0 < M; m0 += MT) {
-    const int m_valid = min(MT, M - m0);
-    float acc[MT];
+    for (int m0 = 0; m0 < M; m0 += MT) {
+        const int m_valid = min(MT, M - m0);
+        float acc[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-    for (int word = lane; word < words; word += 32) {
-        float w[8];
-        dequant_word<FMT>(a, n, word, w);
+        for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+        for (int word = lane; word < words; word += 32) {
+            float w[8];
+            dequant_word<FMT>(a, n, word, w);
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            if (m < m_valid) {
-                float xv[8];
-                Vec8<T>::load(x + (size_t)(m0 + m) * a.K + (size_t)word * 8, xv);
+            for (int m = 0; m < MT; ++m) {
+                if (m < m_valid) {
+                    float xv[8];
+                    Vec8<T>::load(x + (size_t)(m0 + m) * a.K + (size_t)word * 8, xv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[m] = fmaf(xv[j], w[j], acc[m]);
+                    for (int j = 0; j < 8; ++j) acc[m] = fmaf(xv[j], w[j], acc[m]);
+                }
             }
         }
-    }
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        float v = acc[m];
+        for (int m = 0; m < MT; ++m) {
+            float v = acc[m];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && m < m_valid) y[(size_t)(m0 + m) * a.N + n] = from_f32<T>(v);
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && m < m_valid) y[(size_t)(m0 + m) * a.N + n] = from_f32<T>(v);
+        }
     }
-  }
 }
 
 }  // namespace ab2

@@ -155,7 +155,10 @@ int ab2_rms_norm(const void *x_dev, const float *weight_dev, void *out_dev, int 
 /* fused_rope_apply / RopeCache::apply_rotate (crates/aarambh-studio-kernel/src/
  * fused_rope.rs:139-196, crates/aarambh-studio-nn/src/rope.rs:107-126):
  * x [batch, seq, heads, head_dim]; half-split pairs (d, d + head_dim/2); token t
- * uses table row offset + t.  Tables are f32 [max_seq, head_dim/2]. */
+ * uses table row offset + t.  Tables are f32 [max_seq, head_dim/2] whatever `dtype` is: the
+ * reference casts its tables to the model dtype (rope.rs:62-63), so with bf16 or f16 activations
+ * this rotation is slightly more exact than the reference's (the products use unrounded cos / sin);
+ * with f32 activations the two are bit-identical. */
 int ab2_rope_apply(const void *x_dev, void *out_dev, const float *cos_dev, const float *sin_dev,
                    int batch, int seq, int heads, int head_dim, int offset, int max_seq,
                    ab2_dtype dtype, ab2_stream stream);
