@@ -357,7 +357,8 @@ def main():
         tp = pkg.TensorParallel.from_torch_distributed()
     mc, weights = build_large(pkg, torch, cfg, tp_rank=rank, tp_world=world)
     model = pkg.AarambhModel(mc, weights, dtype=torch.bfloat16, max_tokens=max(PROMPT, B, 32), tp=tp)
-    capacity = PROMPT + max(args.warmup, 3) + args.steps + 16
+    e2e_steps = max(32, args.steps // 2)
+    capacity = PROMPT + max(max(args.warmup, 3) + args.steps, 3 + e2e_steps) + 16
     cache = model.empty_kv_cache_with_capacity(capacity, batch=B, dtype="int8")
     gen = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg["vocab"], (B, PROMPT), generator=gen)
@@ -389,7 +390,6 @@ def main():
         ids_dev = torch.empty(B, dtype=torch.int32, device="cuda")
         out_dev = torch.empty(B, dtype=torch.int32, device="cuda")
         ids_host.copy_(state["bufs"][state["n"] % 2].cpu())
-        e2e_steps = max(32, args.steps // 2)
         for b in range(B):
             cache.truncate(PROMPT, b)
 
