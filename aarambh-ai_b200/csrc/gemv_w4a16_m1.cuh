@@ -65,11 +65,14 @@ __device__ __forceinline__ void lds128_if(uint32_t go, uint32_t addr, uint4 &v) 
         : "r"(go), "r"(addr));
 }
 
-// Dynamic shared memory: rings [8][STAGES][1088 B], activations [K] f16, group
+// Dynamic shared memory: rings [8][STAGES][2 x 1088 B], activations [K] f16, group
 // constants [K/128] float2, barriers [8][STAGES].
+// A bulk copy costs its issuing warp (and the SM's copy engine) about 50 cycles whatever its size,
+// so a ring stage holds two consecutive blocks fetched by one copy.
+constexpr int W4M1_COPY_BLOCKS = 2;
 template <int STAGES>
 __host__ __device__ constexpr size_t w4m1_smem_bytes(int K) {
-    return (size_t)W4W_WARPS * STAGES * W4_BLOCK_WORDS * 4 + (size_t)K * 2 + (size_t)(K >> 7) * 8 +
+    return (size_t)W4W_WARPS * STAGES * W4M1_COPY_BLOCKS * W4_BLOCK_WORDS * 4 + (size_t)K * 2 + (size_t)(K >> 7) * 8 +
            (size_t)W4W_WARPS * STAGES * 8;
 }
 
@@ -99,7 +102,7 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     __shared__ float2 warp_part[W4W_WARPS];                 // (sum of squares, largest magnitude)
     __shared__ float2 cta_part[W4W_WARPS][2][8];            // partial sums of cut tiles, rows (r, r + 8)
     __shared__ int cta_cnt[W4M1_LOCAL_TILES];
-    constexpr uint32_t BLOCK_BYTES = W4_BLOCK_WORDS * 4;
+    constexpr uint32_t BLOCK_BYTES = W4_BLOCK_WORDS * 4, STAGE_BYTES = W4M1_COPY_BLOCKS * BLOCK_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, c = lane & 3;
@@ -112,10 +115,10 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     const int b1 = b0 + nblk;
 
     const uint32_t smem0 = smem_addr(smem_raw);
-    const uint32_t xs0 = smem0 + W4W_WARPS * STAGES * BLOCK_BYTES;  // f16 activations
+    const uint32_t xs0 = smem0 + W4W_WARPS * STAGES * STAGE_BYTES;  // f16 activations
     const uint32_t gs0 = xs0 + K * 2;                               // (C2, T) per group
     const uint32_t bars0 = gs0 + G * 8;
-    const uint32_t ring0 = smem0 + warp * STAGES * BLOCK_BYTES, bar0 = bars0 + warp * STAGES * 8;
+    const uint32_t ring0 = smem0 + warp * STAGES * STAGE_BYTES, bar0 = bars0 + warp * STAGES * 8;
     const uint32_t lane0 = lane == 0 ? 1u : 0u;
     if (threadIdx.x < W4M1_LOCAL_TILES) cta_cnt[threadIdx.x] = 0;
     if (lane == 0) {
@@ -132,9 +135,10 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     int to_fetch = nblk;
 #pragma unroll
     for (int j = 0; j < STAGES; ++j) {
-        bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), ring0 + j * BLOCK_BYTES, src, BLOCK_BYTES, bar0 + j * 8);
-        src += W4_BLOCK_WORDS;
-        --to_fetch;
+        bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), ring0 + j * STAGE_BYTES, src,
+                    (uint32_t)min(to_fetch, W4M1_COPY_BLOCKS) * BLOCK_BYTES, bar0 + j * 8);
+        src += W4M1_COPY_BLOCKS * W4_BLOCK_WORDS;
+        to_fetch -= W4M1_COPY_BLOCKS;
     }
 
     // activations (and the residual) come from the preceding kernel
@@ -319,8 +323,8 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     const int cta_tile0 = (cta_w0 * base + min(cta_w0, rem)) / G;
 
     int tile = b0 / G, g = b0 - tile * G;
-    uint32_t cur = ring0, bar = bar0, parity = 0;
-    const uint32_t ring_end = ring0 + STAGES * BLOCK_BYTES;
+    uint32_t cur = ring0, bar = bar0, parity = 0, second = 0;  // second: the stage's second block is next
+    const uint32_t ring_end = ring0 + STAGES * STAGE_BYTES;
     uint4 xw[4];
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) xw[wi] = make_uint4(0u, 0u, 0u, 0u);
@@ -332,7 +336,7 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
         uint32_t xaddr = xlane + g * 256, gaddr = gs0 + g * 8;
 
         for (int it = 0; it < n; ++it) {
-            if (!mbar_wait_addr(bar, parity)) {
+            if (!second && !mbar_wait_addr(bar, parity)) {
                 if (lane == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
                 return;
             }
@@ -372,15 +376,19 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
             acc_a = fmaf(sa, (d[0] + d2[0]) - fmaf(-nza, T, C2), acc_a);
             acc_b = fmaf(sb, (d[2] + d2[2]) - fmaf(-nzb, T, C2), acc_b);
 
-            // Refill this stage with the block STAGES ahead: every lane's loads of it
-            // were issued at the top of the step and have been consumed above.
-            __syncwarp();
-            bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur, src, BLOCK_BYTES, bar);
-            src += W4_BLOCK_WORDS;
-            --to_fetch;
+            // After its second block, refill the stage with the two blocks STAGES stages ahead:
+            // every lane's loads of it were issued at the top of the steps and have been consumed.
             cur += BLOCK_BYTES;
-            bar += 8;
-            if (cur == ring_end) { cur = ring0; bar = bar0; parity ^= 1; }
+            if (second) {
+                __syncwarp();
+                bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur - STAGE_BYTES, src,
+                            (uint32_t)min(to_fetch, W4M1_COPY_BLOCKS) * BLOCK_BYTES, bar);
+                src += W4M1_COPY_BLOCKS * W4_BLOCK_WORDS;
+                to_fetch -= W4M1_COPY_BLOCKS;
+                bar += 8;
+                if (cur == ring_end) { cur = ring0; bar = bar0; parity ^= 1; }
+            }
+            second ^= 1u;
         }
         b += n;
 

@@ -136,8 +136,8 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int q = 0; q < 4; ++q)
-            for (int i = 0; i < DG_WSLOTS; ++i) { bar_init(&sh->wfull[q][i], 2); bar_init(&sh->wempty[q][i], 64); }
-        for (int i = 0; i < DG_STAGES; ++i) { bar_init(&sh->afull[i], 128); bar_init(&sh->sempty[i], 1); }
+            for (int i = 0; i < DG_WSLOTS; ++i) { bar_init(&sh->wfull[q][i], 2); bar_init(&sh->wempty[q][i], 2); }
+        for (int i = 0; i < DG_STAGES; ++i) { bar_init(&sh->afull[i], 4); bar_init(&sh->sempty[i], 1); }
         for (int i = 0; i < DG_XSTAGES; ++i) { bar_init(&sh->xfull[i], 1); bar_init(&sh->xempty[i], 1); }
         for (int i = 0; i < DG_ACC; ++i) { bar_init(&sh->accfull[i], 1); bar_init(&sh->accempty[i], 4); }
         sh->failed = 0;
@@ -236,7 +236,9 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             const uint32_t pr = bw[256 + r];
             if (half == 0) sh->params[use % DG_PARAM_BUFS][t] = pr;
             const uint32_t nz2 = __byte_perm(pr, pr, 0x3232);  // bf16x2 -(128 + zero) of this channel
-            bar_arrive(&sh->wempty[q][ws]);
+            // one arrival per warp: arrivals on one mbarrier serialise on its word
+            __syncwarp();
+            if (lane == 0) bar_arrive(&sh->wempty[q][ws]);
             // refill the slot released one unit ago (both warps of the pair have read it by now, or will shortly)
             if (lane == 0 && use >= 1 && (int)use - 1 + DG_WSLOTS < n_units) {
                 const uint32_t pu = use - 1;
@@ -258,7 +260,8 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                 *reinterpret_cast<uint4 *>(arow + ((c ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             }
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            bar_arrive(&sh->afull[s]);
+            __syncwarp();
+            if (lane == 0) bar_arrive(&sh->afull[s]);
         }
     } else {
         // ---------------------------------------------------------- epilogue

@@ -190,18 +190,18 @@ static cudaError_t launch_w4a16_m1(const ab2_qweight *w, const __nv_bfloat16 *x,
     if (peers) {  // tensor parallel: the input is the residual plus the exchanged partial sums (norm fused)
         if constexpr (EPI == W4_EPI_STORE || EPI == W4_EPI_SWIGLU) {
             if (w->K <= 8192)
-                return launch_w4a16_m1_inst<EPI, 5, 4, true, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s, peers, x_out);
-            return launch_w4a16_m1_inst<EPI, 4, 8, true, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s, peers, x_out);
+                return launch_w4a16_m1_inst<EPI, 3, 4, true, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s, peers, x_out);
+            return launch_w4a16_m1_inst<EPI, 2, 8, true, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s, peers, x_out);
         } else {
             return cudaErrorInvalidValue;
         }
     }
     if (w->K <= 8192) {
-        if (norm_w) return launch_w4a16_m1_inst<EPI, 5, 4, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
-        return launch_w4a16_m1_inst<EPI, 5, 4, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+        if (norm_w) return launch_w4a16_m1_inst<EPI, 3, 4, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+        return launch_w4a16_m1_inst<EPI, 3, 4, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
     }
-    if (norm_w) return launch_w4a16_m1_inst<EPI, 4, 8, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
-    return launch_w4a16_m1_inst<EPI, 4, 8, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+    if (norm_w) return launch_w4a16_m1_inst<EPI, 2, 8, true>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
+    return launch_w4a16_m1_inst<EPI, 2, 8, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
 }
 
 constexpr int W4M1_MAX_K = 16384;
