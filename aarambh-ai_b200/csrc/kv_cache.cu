@@ -29,13 +29,17 @@ template <typename T, int KVD>
 __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T *__restrict__ v_in,
                                  long long in_stride, int S, int row0, const float *__restrict__ cos_t,
                                  const float *__restrict__ sin_t, const int *__restrict__ rope_pos,
-                                 T *q_rot, int q_heads) {
+                                 T *q_rot, int q_heads, int tpb) {
     extern __shared__ float sh[];  // [2][hd] values, then 2 * 8 reduction slots
     pdl_wait();  // inputs come from the preceding kernel of the step
     pdl_launch_dependents();
     const int hd = kv.hd, half = hd >> 1;
-    const int s = blockIdx.x, head = blockIdx.y, rrow = blockIdx.z, row = kv_row(kv, row0, rrow);
+    const int head = blockIdx.y, rrow = blockIdx.z, row = kv_row(kv, row0, rrow);
     const int d = threadIdx.x;
+    // a block serves `tpb` consecutive tokens of its (row, head): one block per token leaves a long
+    // prefill bound by block launches (every branch below is uniform over the block)
+    for (int s = blockIdx.x * tpb; s < min(S, (int)(blockIdx.x + 1) * tpb); ++s) {
+    if (s != blockIdx.x * tpb) __syncthreads();  // the previous token's values in shared memory have been read
     if (head >= kv.kvh) {
         // blocks past the KV heads rotate one query head in place (same row stride as k / v)
         T *q = q_rot + ((size_t)rrow * S + s) * (size_t)in_stride + (size_t)(head - kv.kvh) * hd;
@@ -46,10 +50,10 @@ __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T 
         float o1, o2;
         rope_rotate(sh[i], sh[half + i], cos_t[(size_t)p * half + i], sin_t[(size_t)p * half + i], o1, o2);
         q[d] = from_f32<T>(d < half ? o1 : o2);
-        return;
+        continue;
     }
     const int pos = kv.lens[row] + s;
-    if (pos >= kv.cap) return;  // capacity is checked on the host; never write out of range
+    if (pos >= kv.cap) continue;  // capacity is checked on the host; never write out of range
     const size_t in_off = ((size_t)rrow * S + s) * (size_t)in_stride + (size_t)head * hd;
     float kval = to_f32(k_in[in_off + d]);
     const float vval = to_f32(v_in[in_off + d]);
@@ -99,6 +103,7 @@ __global__ void kv_append_kernel(KvView kv, const T *__restrict__ k_in, const T 
             kv.ks[soff] = kscale;
             kv.vs[soff] = vscale;
         }
+    }
     }
 }
 
@@ -150,15 +155,16 @@ static int launch_append(ab2_kv *kv, int layer, const T *k, const T *v, long lon
                          const int *rope_pos, T *q_rot, int q_heads, cudaStream_t s) {
     KvView view = kv_view(kv, layer);
     if (q_rot == nullptr || cos_t == nullptr) q_heads = 0;
-    dim3 grid(S, kv->kvh + q_heads, nrows);
+    const int tpb = S >= 64 ? 8 : 1;  // tokens per block
+    dim3 grid((S + tpb - 1) / tpb, kv->kvh + q_heads, nrows);
     size_t smem = (2 * (size_t)kv->hd + 16) * sizeof(float);
     cudaError_t e;
     if (kv->dtype == AB2_KV_F32)
-        e = launch_kernel(kv_append_kernel<T, AB2_KV_F32>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_F32>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads, tpb);
     else if (kv->dtype == AB2_KV_BF16)
-        e = launch_kernel(kv_append_kernel<T, AB2_KV_BF16>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_BF16>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads, tpb);
     else
-        e = launch_kernel(kv_append_kernel<T, AB2_KV_INT8>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads);
+        e = launch_kernel(kv_append_kernel<T, AB2_KV_INT8>, grid, dim3(kv->hd), smem, s, view, k, v, in_stride, S, row0, cos_t, sin_t, rope_pos, q_rot, q_heads, tpb);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "KV append launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }

@@ -86,15 +86,27 @@ __global__ void add_f32_projection_kernel(__nv_bfloat16 *x, const float *p, size
 
 // SwiGLU over the output of the interleaved gate|up weight: columns come in
 // blocks of 16 = 8 gate values followed by the 8 matching up values.
-__global__ void swiglu_interleaved8_kernel(const __nv_bfloat16 *gu, __nv_bfloat16 *out, int ffn, size_t n) {
+__global__ void swiglu_interleaved8_kernel(const __nv_bfloat16 *gu, __nv_bfloat16 *out, int ffn, size_t n8) {
     pdl_wait();  // inputs come from the preceding kernel of the step
     pdl_launch_dependents();
+    // one thread per block of 16 columns: 16 bytes of gate, 16 bytes of up, 16 bytes out
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    size_t tok = i / ffn;
-    int j = (int)(i % ffn);
-    const __nv_bfloat16 *row = gu + tok * 2 * (size_t)ffn + (size_t)(j >> 3) * 16 + (j & 7);
-    out[i] = __float2bfloat16_rn(swiglu_value(__bfloat162float(row[0]), __bfloat162float(row[8])));
+    if (i >= n8) return;
+    const int per_row = ffn >> 3;
+    const size_t tok = i / per_row;
+    const int jb = (int)(i % per_row);
+    const uint4 *src = reinterpret_cast<const uint4 *>(gu + tok * 2 * (size_t)ffn + (size_t)jb * 16);
+    const uint4 g = src[0], u = src[1];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+        const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+        o[k] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(swiglu_value(g0, u0))) |
+               ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(swiglu_value(g1, u1))) << 16);
+    }
+    *reinterpret_cast<uint4 *>(out + tok * (size_t)ffn + (size_t)jb * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // [world][rows][vn] (all-gathered vocabulary shards) -> [rows][world * vn]
@@ -245,9 +257,9 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
             STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
             {
-                size_t n = (size_t)T * c.ffn_hidden;
-                cudaError_t e = launch_kernel(swiglu_interleaved8_kernel, dim3((unsigned)ceil_div(n, 256)), dim3(256), 0, s,
-                                              (const __nv_bfloat16 *)m->gu, (__nv_bfloat16 *)m->hid, (int)c.ffn_hidden, n);
+                size_t n8 = (size_t)T * (c.ffn_hidden / 8);
+                cudaError_t e = launch_kernel(swiglu_interleaved8_kernel, dim3((unsigned)ceil_div(n8, 256)), dim3(256), 0, s,
+                                              (const __nv_bfloat16 *)m->gu, (__nv_bfloat16 *)m->hid, (int)c.ffn_hidden, n8);
                 if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "SwiGLU launch failed: %s", cudaGetErrorString(e));
             }
             STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
