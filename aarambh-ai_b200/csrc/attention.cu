@@ -275,6 +275,9 @@ static bool decode_on_mma(const ab2_kv *kv) {
 static int decode_split_count(const ab2_kv *kv, int nrows, int max_len, int max_splits, bool mma) {
     const int sms = device_sm_count(), units = nrows * kv->kvh;
     if (mma) {
+        // short contexts with at least one (row, KV head) per SM: one CTA each and no merge launch
+        // (32 rows x 512 tokens: 4.35 ms per decode step against 4.62 with four splits)
+        if (units >= sms && max_len <= 1024) return 1;
         const int want = (sms * 6 + units - 1) / units;
         return std::max(1, std::min(std::min(want, (max_len + 63) / 64), max_splits));
     }
