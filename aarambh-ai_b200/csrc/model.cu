@@ -141,8 +141,9 @@ static bool decode_attention_on_tensor_cores(const ab2_kv *kv, int nrows, int ma
 // normalises inside the GEMV; otherwise the norm is its own launch into m->xn.
 // epi: 0 plain projection (any format), 2 SwiGLU over an interleaved gate|up weight.
 static int norm_linear(ab2_model *m, const ab2_qweight *w, const void *x, const float *norm_w, int T, void *out,
-                       int epi, cudaStream_t s) {
+                       int epi, cudaStream_t s, bool normed = false) {
     const ab2_model_config &c = m->cfg;
+    if (normed) return qlinear_dispatch(w, m->xn, T, m->dtype, out, s);  // m->xn already holds RMSNorm(x; norm_w)
     if (m->fused_epilogues && qlinear_w4a16_norm_fusable(w, m->dtype, T))
         return qlinear_w4a16_norm(w, x, norm_w, c.rms_eps, out, epi, s);
     STEP(launch_rms_norm(x, norm_w, m->xn, T, c.d_model, c.rms_eps, m->dtype, s));
@@ -176,10 +177,12 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         pending = false;
         return rc2;
     };
+    bool xn_ready = false;  // the preceding layer's last residual add also wrote RMSNorm(x; norm1) of this layer
     for (int l = 0; l < c.n_layers; ++l) {
         LayerWeights &L = m->layers[l];
         if (pending) STEP(consume(L.wqkv, L.norm1, m->qkv, 0));
-        else STEP(norm_linear(m, L.wqkv, xcur, L.norm1, T, m->qkv, 0, s));
+        else STEP(norm_linear(m, L.wqkv, xcur, L.norm1, T, m->qkv, 0, s, xn_ready));
+        xn_ready = false;
         int max_len = len_hint;
         if (S == 1 && max_len <= 0)
             for (int i = 0; i < nrows; ++i) max_len = std::max(max_len, kv->lens_host[kv_row_host(kv, row0, i)] + 1);
@@ -253,8 +256,7 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
             // tokens on this measured faster than the residual / SwiGLU epilogues of the decode GEMM:
             // 6330 against 6120 tok/s at 32 rows, 7360 against 6740 at 64)
             STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
-            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
-            STEP(launch_rms_norm(m->x, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
+            STEP(launch_add_rms_norm(m->x, m->proj, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
             STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
             {
                 size_t n8 = (size_t)T * (c.ffn_hidden / 8);
@@ -263,7 +265,12 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
                 if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "SwiGLU launch failed: %s", cudaGetErrorString(e));
             }
             STEP(qlinear_dispatch(L.part[6], m->hid, T, m->dtype, m->proj, s));
-            STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+            if (l + 1 < c.n_layers) {  // the add and the next layer's first normalisation in one launch
+                STEP(launch_add_rms_norm(m->x, m->proj, m->layers[l + 1].norm1, m->xn, T, d, c.rms_eps, m->dtype, s));
+                xn_ready = true;
+            } else {
+                STEP(launch_add(m->x, m->proj, m->x, (size_t)T * d, m->dtype, s));
+            }
         } else if (m->fused_epilogues) {
             STEP(qlinear_w4a16_mma_add(L.part[3], m->attn, T, m->x, m->x, s));
             STEP(norm_linear(m, L.wgu, m->x, L.norm2, T, m->hid, 2, s));

@@ -44,13 +44,16 @@ __global__ void rms_norm_kernel(const T *__restrict__ x, const float *__restrict
 
 // bf16 rows with d % 8 == 0: every thread owns 8-element vectors, all loads of a
 // row are in flight at once (decode rows are latency-bound, not bandwidth-bound).
-__global__ void rms_norm_bf16_vec_kernel(const __nv_bfloat16 *__restrict__ x, const float *__restrict__ w,
+// ADD: the row is first replaced by x + p (the residual add of the decoder, rounded to bf16 as the
+// stand-alone add does) and the normalisation reads the new row: one launch for the pair.
+template <bool ADD>
+__global__ void rms_norm_bf16_vec_kernel(__nv_bfloat16 *x, const __nv_bfloat16 *p, const float *__restrict__ w,
                                          __nv_bfloat16 *out, int d, float eps) {
     __shared__ float warp_sums[32];
     __shared__ float inv_shared;
     pdl_wait();
     pdl_launch_dependents();
-    const uint4 *row = reinterpret_cast<const uint4 *>(x + (size_t)blockIdx.x * d);
+    uint4 *row = reinterpret_cast<uint4 *>(x + (size_t)blockIdx.x * d);
     const int nvec = d >> 3;
     uint4 v[2];
     float sum = 0.f;
@@ -58,6 +61,19 @@ __global__ void rms_norm_bf16_vec_kernel(const __nv_bfloat16 *__restrict__ x, co
     for (int it = 0; it < 2; ++it) {
         const int i = threadIdx.x + it * blockDim.x;
         v[it] = i < nvec ? row[i] : make_uint4(0, 0, 0, 0);
+        if (ADD && i < nvec) {
+            const uint4 q = reinterpret_cast<const uint4 *>(p + (size_t)blockIdx.x * d)[i];
+            const uint32_t a4[4] = {v[it].x, v[it].y, v[it].z, v[it].w}, b4[4] = {q.x, q.y, q.z, q.w};
+            uint32_t s4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = __fadd_rn(__uint_as_float(a4[j] << 16), __uint_as_float(b4[j] << 16));
+                const float hi = __fadd_rn(__uint_as_float(a4[j] & 0xffff0000u), __uint_as_float(b4[j] & 0xffff0000u));
+                s4[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+            }
+            v[it] = make_uint4(s4[0], s4[1], s4[2], s4[3]);
+            row[i] = v[it];
+        }
         const uint32_t r[4] = {v[it].x, v[it].y, v[it].z, v[it].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -102,8 +118,9 @@ int launch_rms_norm(const void *x, const float *w, void *out, int rows, int d, f
                     ab2_dtype dtype, cudaStream_t s) {
     if (dtype == AB2_BF16 && d % 8 == 0 && d / 8 <= 2048 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0) {
         int threads = std::min(1024, ((d / 8 + 1) / 2 + 31) / 32 * 32);
-        cudaError_t e = launch_kernel(rms_norm_bf16_vec_kernel, dim3(rows), dim3(threads), 0, s,
-                                      (const __nv_bfloat16 *)x, w, (__nv_bfloat16 *)out, d, eps);
+        cudaError_t e = launch_kernel(rms_norm_bf16_vec_kernel<false>, dim3(rows), dim3(threads), 0, s,
+                                      (__nv_bfloat16 *)const_cast<void *>(x), (const __nv_bfloat16 *)nullptr, w,
+                                      (__nv_bfloat16 *)out, d, eps);
         if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "RMSNorm launch failed: %s", cudaGetErrorString(e));
         return AB2_OK;
     }
@@ -115,6 +132,23 @@ int launch_rms_norm(const void *x, const float *w, void *out, int rows, int d, f
     }
     AB2_LAUNCH_CHECK();
     return AB2_OK;
+}
+
+// x += p (row-wise, rounded to the activation type), then out = RMSNorm(x; w): one launch where the
+// vector kernel applies, else the two launches it replaces.
+int launch_add_rms_norm(void *x, const void *p, const float *w, void *out, int rows, int d, float eps,
+                        ab2_dtype dtype, cudaStream_t s) {
+    if (dtype == AB2_BF16 && d % 8 == 0 && d / 8 <= 2048 &&
+        (((uintptr_t)x | (uintptr_t)p | (uintptr_t)out | (uintptr_t)w) & 15) == 0) {
+        int threads = std::min(1024, ((d / 8 + 1) / 2 + 31) / 32 * 32);
+        cudaError_t e = launch_kernel(rms_norm_bf16_vec_kernel<true>, dim3(rows), dim3(threads), 0, s, (__nv_bfloat16 *)x,
+                                      (const __nv_bfloat16 *)p, w, (__nv_bfloat16 *)out, d, eps);
+        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "add + RMSNorm launch failed: %s", cudaGetErrorString(e));
+        return AB2_OK;
+    }
+    int rc = launch_add(x, p, x, (size_t)rows * d, dtype, s);
+    if (rc != AB2_OK) return rc;
+    return launch_rms_norm(x, w, out, rows, d, eps, dtype, s);
 }
 
 // ---- RoPE ------------------------------------------------------------------

@@ -24,6 +24,8 @@ int launch_rms_norm(const void *x, const float *w, void *out, int rows, int d, f
 int launch_swiglu_fused(const void *gu, void *out, int tokens, int ffn, ab2_dtype dtype,
                         cudaStream_t s);
 int launch_add(const void *a, const void *b, void *out, size_t n, ab2_dtype dtype, cudaStream_t s);
+int launch_add_rms_norm(void *x, const void *p, const float *w, void *out, int rows, int d, float eps,
+                        ab2_dtype dtype, cudaStream_t s);
 int launch_argmax(const void *logits, int rows, int vocab, ab2_dtype dtype, uint32_t *out,
                   cudaStream_t s);
 int launch_embedding(const ab2_qweight *table, const uint32_t *ids, int tokens, void *out,
