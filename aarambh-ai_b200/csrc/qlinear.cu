@@ -326,6 +326,8 @@ int qlinear_w4a16_norm_peer(const ab2_qweight *w, const void *x, const float *no
 
 int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 bool qlinear_i8_stream_eligible(const ab2_qweight *w, ab2_dtype dtype, int M);
+bool qlinear_q4km_stream_eligible(const ab2_qweight *w, ab2_dtype dtype, int M);
+int qlinear_q4km_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
 bool qlinear_i8_tc_eligible(const ab2_qweight *w, ab2_dtype dtype, int M);
 int qlinear_i8_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s);
@@ -342,6 +344,8 @@ int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype
     if (qlinear_i8_stream_eligible(w, dtype, M)) return qlinear_i8_stream(w, x, M, y, s);
     // more tokens: tcgen05 GEMM, the codes converted to bf16 on the way into the operand stages
     if (qlinear_i8_tc_eligible(w, dtype, M)) return qlinear_i8_tc(w, x, M, y, s);
+    // Q4_K_M blocks (GGUF-loaded models), bf16 activations, a few tokens: the streaming GEMV over the two planes
+    if (qlinear_q4km_stream_eligible(w, dtype, M)) return qlinear_q4km_stream(w, x, M, y, s);
     return qlinear_generic(w, x, M, dtype, y, s);
 }
 

@@ -9,6 +9,7 @@ launch reads from HBM.
     python microbench.py attention [--cases 8x16384] INT8-KV flash-decode (HBM GB/s)
     python microbench.py prefill_attention [--cases 1x512] causal attention of a prompt over the INT8 cache
     python microbench.py gemv|gemm --fmt int8             the same two for INT8 per-channel weights
+    python microbench.py gemv --fmt q4km                  the GEMV over Q4_K_M-style blocks
     python microbench.py step      [--layers 2] [--ctx 512] one-token decoder step of a short
                                                    Large-shaped stack (a few hundred MB on the device: the
                                                    case to capture the step's kernels under a profiler)
@@ -105,11 +106,22 @@ def random_int8(pkg, N, K, seed):
     return pkg.QuantLinear.quantise(w, "int8_channel")
 
 
+def random_q4km(pkg, N, K, seed):
+    """N(0, 0.02) weights quantised to Q4_K_M-style blocks of 256."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn((N, K), generator=g, device="cuda") * 0.02
+    return pkg.QuantLinear.quantise(w, "q4_k_m")
+
+
 def bench_gemv_int8(pkg, args):
     stream = torch.cuda.Stream()
+    q4 = args.fmt == "q4km"
     for K, N in SHAPES:
-        copies = 1 if args.profile else max(2, math.ceil(400e6 / (N * K)))
-        lins = [random_int8(pkg, N, K, 2 + i) for i in range(copies)]
+        if q4 and K % 256:
+            continue
+        wbytes = K * N // 2 + 4 * N * (K // 256) if q4 else K * N + 4 * N
+        copies = 1 if args.profile else max(2, math.ceil(400e6 / wbytes))
+        lins = [(random_q4km if q4 else random_int8)(pkg, N, K, 2 + i) for i in range(copies)]
         for M in args.m:
             x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
             if args.profile:
@@ -119,8 +131,10 @@ def bench_gemv_int8(pkg, args):
                 print("profiled case", K, N, M)
                 return
             t = time_graph(lambda: [lin(x) for lin in lins], 5, stream) / copies
-            byt = K * N + 4 * N + 2 * M * (K + N)
-            print(json.dumps({"kernel": "gemv_i8_stream_kernel" if M <= 8 else "gemm_i8_tc_kernel", "K": K, "N": N, "M": M,
+            byt = wbytes + 2 * M * (K + N)
+            name = ("gemv_q4km_stream_kernel" if M <= 8 else "gemv_generic_kernel") if q4 else \
+                   ("gemv_i8_stream_kernel" if M <= 8 else "gemm_i8_tc_kernel")
+            print(json.dumps({"kernel": name, "K": K, "N": N, "M": M,
                               "us": round(t * 1e6, 2), "GBs": round(byt / t / 1e9, 1),
                               "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}), flush=True)
         del lins
@@ -277,7 +291,7 @@ def main():
     ap.add_argument("--cases", default=None)
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--shape", default=None, help="K,N: restrict gemv / gemm to one weight shape")
-    ap.add_argument("--fmt", default="w4a16", choices=["w4a16", "int8"], help="weight format of gemv / gemm")
+    ap.add_argument("--fmt", default="w4a16", choices=["w4a16", "int8", "q4km"], help="weight format of gemv (gemm: w4a16, int8)")
     args = ap.parse_args()
     pkg = import_package()
     torch.cuda.set_device(0)
@@ -286,7 +300,7 @@ def main():
         SHAPES[:] = [(k, n)]
     if args.what == "gemv":
         args.m = [int(v) for v in (args.m or "1,4,16").split(",")]
-        (bench_gemv_int8 if args.fmt == "int8" else bench_gemv)(pkg, args)
+        (bench_gemv_int8 if args.fmt in ("int8", "q4km") else bench_gemv)(pkg, args)
     elif args.what == "gemm":
         args.m = [int(v) for v in (args.m or "512,2048,8192").split(",")]
         bench_gemm(pkg, args)

@@ -115,6 +115,22 @@ def test_int8_per_channel_decode_and_prefill(K, N, Ms):
         assert _sampled(lin, dense, K, M, 13 + M) < TOL, M
 
 
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 14336), (1024, 400)])
+def test_q4km_blocks_decode_gemv(K, N):
+    """Q4_K_M-style blocks (gguf_quant.rs:39-49), bf16 activations, 1..8 tokens: the streaming GEMV over
+    the code and parameter planes; the dequantised weight is bit-exact with the oracle on a slice."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = torch.randn((N, K), generator=g, device="cuda") * 0.02
+    lin = pkg().QuantLinear.quantise(w, "q4_k_m")
+    dense = lin.dequantise().cpu().numpy()
+    head = w[:16].cpu().numpy()
+    assert np.array_equal(dense[:16], orc.decode_q4km_tensor(orc.encode_q4km_tensor(head), (16, K)))
+    del w
+    for M in (1, 3, 8):
+        assert _sampled(lin, dense, K, M, 21 + M) < TOL, M
+    assert pkg().device_status() == 0
+
+
 # ---------------------------------------------------------------------------
 # INT8-KV decode attention at long contexts
 # ---------------------------------------------------------------------------
