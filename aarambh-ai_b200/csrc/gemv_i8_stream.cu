@@ -193,7 +193,9 @@ int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaS
     }
     // two 16-row tiles per CTA once that still leaves every SM a few CTAs (the activations are staged per CTA)
     const int tiles = (w->N + 15) / 16;
-    const bool two = false;  // measured: two tiles per CTA is slower at every shape (0.47 against 0.59 of HBM on 4096 x 14336)
+    // measured: two tiles per CTA are slower up to 4 tokens (one token: 0.47 against 0.59 of HBM on
+    // 4096 x 14336) and faster at 8, where staging the activations per CTA weighs most (32.7 against 44.7 us)
+    const bool two = M >= 8;
     cudaError_t e = two ? launch_kernel(gemv_i8_stream_kernel<2>, dim3((tiles + 1) / 2), dim3(256), smem, s, (const int8_t *)w->codes,
                                         (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M)
                         : launch_kernel(gemv_i8_stream_kernel<1>, dim3(tiles), dim3(256), smem, s, (const int8_t *)w->codes,
