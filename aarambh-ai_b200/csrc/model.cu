@@ -303,6 +303,10 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         const int vn = c.vocab / m->tp->world;
         if (pending) STEP(consume(m->lm_head, m->final_norm, m->lg_local, 0));
         else STEP(norm_linear(m, m->lm_head, hidden, m->final_norm, rows, m->lg_local, 0, s));
+        if (!logits && argmax_out && rows == nrows && rows <= AB2_TP_ARGMAX_ROWS && m->tp->attached) {
+            // only the sampled token is wanted: local argmax, one (value, index) pair per rank over NVLink
+            return tp_peer_argmax(m->tp, m->lg_local, rows, vn, m->dtype, argmax_out, s);
+        }
         void *gathered = rows == 1 ? lg : m->lg_all;
         STEP(tp_all_gather(m->tp, m->lg_local, gathered, (size_t)rows * vn, m->dtype, s));
         if (rows > 1) {

@@ -169,6 +169,74 @@ tp_peer_deposit_kernel(const float *partial, size_t count, const ab2_tp_peer_des
     }
 }
 
+// Key of the argmax: monotone in the f32 total order, ties to the larger index (the last maximum,
+// crates/aarambh-studio-inference/src/sampler.rs:217-224).
+__device__ __forceinline__ long long tp_argmax_key(float v, uint32_t idx) {
+    int b = __float_as_int(v);
+    b ^= (int)(((unsigned)(b >> 31)) >> 1);
+    return ((long long)b << 32) | idx;
+}
+
+// One CTA per row: argmax of this rank's shard, then one (value, index) pair to every rank (two
+// tagged 8-byte words), a bounded wait for the world's pairs, and the same winner on every rank.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+tp_argmax_exchange_kernel(const ab2_tp_peer_desc *desc, const T *__restrict__ logits, int vn, uint32_t *out, int *status) {
+    __shared__ long long warp_best[32];
+    pdl_wait();  // the logits come from the preceding kernel
+    pdl_launch_dependents();
+    const ab2_tp_peer_desc d = *desc;
+    const T *row = logits + (size_t)blockIdx.x * vn;
+    const uint32_t base = (uint32_t)d.rank * (uint32_t)vn;
+    long long best = LLONG_MIN;
+    for (int i = threadIdx.x; i < vn; i += blockDim.x) best = max(best, tp_argmax_key(to_f32(row[i]), base + (uint32_t)i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    best = threadIdx.x < (blockDim.x >> 5) ? warp_best[threadIdx.x] : LLONG_MIN;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    const uint32_t e = *d.argmax_epoch + 1;
+    const size_t slot = d.argmax_off + (size_t)(e & 1u) * d.world * (2 * AB2_TP_ARGMAX_ROWS) + 2 * (size_t)blockIdx.x;
+    // lane p stores this rank's pair with rank p, then waits for rank p's pair in the local inbox
+    bool ok = true;
+    long long theirs = LLONG_MIN;
+    if ((int)threadIdx.x < d.world) {
+        const int p = (int)threadIdx.x;
+        unsigned long long *dst = d.inbox[p] + slot + (size_t)d.rank * (2 * AB2_TP_ARGMAX_ROWS);
+        tp_ll_store(dst, ((unsigned long long)e << 32) | (uint32_t)(best >> 32));
+        tp_ll_store(dst + 1, ((unsigned long long)e << 32) | (uint32_t)best);
+        const unsigned long long *src = d.inbox[d.rank] + slot + (size_t)p * (2 * AB2_TP_ARGMAX_ROWS);
+        unsigned long long hi = 0, lo = 0, t0 = 0;
+        for (int spin = 0;; ++spin) {
+            tp_ll_load2(src, hi, lo);
+            if ((uint32_t)(hi >> 32) == e && (uint32_t)(lo >> 32) == e) break;
+            if ((spin & 15) == 15) {
+                const unsigned long long now = tp_wall_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > d.wait_limit_ns) { ok = false; break; }
+            }
+        }
+        theirs = (long long)(((unsigned long long)(uint32_t)hi << 32) | (uint32_t)lo);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) theirs = max(theirs, __shfl_xor_sync(0xffffffffu, theirs, o));
+    if (threadIdx.x != 0) return;
+    if (!ok) {  // a peer's pair did not arrive within the limit: the exchange count stays (ab2_tp_peer_reset)
+        atomicExch(status, (int)AB2_ERR_TIMEOUT);
+        return;
+    }
+    out[blockIdx.x] = (uint32_t)theirs;
+    if (atomicAdd(d.argmax_done, 1u) == gridDim.x - 1) {  // every row has read the exchange count: close the exchange
+        *d.argmax_done = 0;
+        __threadfence();
+        *d.argmax_epoch = e;
+    }
+}
+
 }  // namespace
 
 bool tp_peer_ready(const ab2_tp *tp, size_t count) {
@@ -194,6 +262,24 @@ int tp_peer_deposit(ab2_tp *tp, const float *partial_f32, size_t count, cudaStre
     cudaError_t e = launch_kernel(tp_peer_deposit_kernel, dim3(ctas), dim3(256), 0, s, partial_f32, count,
                                   (const ab2_tp_peer_desc *)tp->desc_dev);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "peer deposit launch failed: %s", cudaGetErrorString(e));
+    return AB2_OK;
+}
+
+int tp_peer_argmax(ab2_tp *tp, const void *logits_local, int rows, int vn, ab2_dtype dtype, uint32_t *out, cudaStream_t s) {
+    AB2_REQUIRE(tp && tp->world > 1 && tp->attached, AB2_ERR_BAD_ARG, "the peer exchange is not attached");
+    AB2_REQUIRE(rows >= 1 && rows <= AB2_TP_ARGMAX_ROWS, AB2_ERR_CAPACITY, "the argmax exchange serves up to %d rows, got %d",
+                AB2_TP_ARGMAX_ROWS, rows);
+    int *status = nullptr;
+    int rc = device_status_word(&status);
+    if (rc != AB2_OK) return rc;
+    const ab2_tp_peer_desc *desc = tp->desc_dev;
+    cudaError_t e;
+    switch (dtype) {
+    case AB2_F32: e = launch_kernel(tp_argmax_exchange_kernel<float>, dim3(rows), dim3(1024), 0, s, desc, (const float *)logits_local, vn, out, status); break;
+    case AB2_F16: e = launch_kernel(tp_argmax_exchange_kernel<__half>, dim3(rows), dim3(1024), 0, s, desc, (const __half *)logits_local, vn, out, status); break;
+    default: e = launch_kernel(tp_argmax_exchange_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, s, desc, (const __nv_bfloat16 *)logits_local, vn, out, status); break;
+    }
+    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "argmax exchange launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
 
@@ -265,9 +351,13 @@ AB2_API int ab2_tp_all_reduce(ab2_tp *tp, void *buf_dev, size_t count, ab2_dtype
     return tp_all_reduce(tp, buf_dev, count, dtype, (cudaStream_t)stream);
 }
 
-// Layout of a rank's block: inbox [2][world][max_elems] 8-byte words, then the epoch and done words.
+// Layout of a rank's block: inbox [2][world][max_elems] 8-byte words, then 32 words of counters
+// (epoch, done, argmax epoch, argmax done), then the argmax inbox [2][world][2 * AB2_TP_ARGMAX_ROWS] words.
 static size_t peer_inbox_words(int world, size_t max_elems) { return 2 * (size_t)world * max_elems; }
-static size_t peer_block_bytes(int world, size_t max_elems) { return peer_inbox_words(world, max_elems) * 8 + 256; }
+static size_t peer_argmax_off(int world, size_t max_elems) { return peer_inbox_words(world, max_elems) + 32; }
+static size_t peer_block_bytes(int world, size_t max_elems) {
+    return (peer_argmax_off(world, max_elems) + 2 * (size_t)world * 2 * AB2_TP_ARGMAX_ROWS) * 8;
+}
 
 static int peer_fill_desc(ab2_tp *tp, void *const *blocks) {
     ab2_tp_peer_desc d;
@@ -276,6 +366,9 @@ static int peer_fill_desc(ab2_tp *tp, void *const *blocks) {
     uint32_t *words = (uint32_t *)((unsigned long long *)tp->local_block + peer_inbox_words(tp->world, tp->max_elems));
     d.epoch = words;
     d.done = words + 1;
+    d.argmax_epoch = words + 2;
+    d.argmax_done = words + 3;
+    d.argmax_off = peer_argmax_off(tp->world, tp->max_elems);
     d.rank = tp->rank; d.world = tp->world; d.max_elems = tp->max_elems;
     d.wait_limit_ns = tp->wait_limit_ns;
     if (!tp->desc_dev) AB2_CUDA(cudaMalloc((void **)&tp->desc_dev, sizeof(d)));

@@ -22,7 +22,12 @@ struct ab2_tp_peer_desc {
     int rank, world;
     unsigned long long max_elems;
     unsigned long long wait_limit_ns;     // how long a reader waits for a peer's words (default two seconds)
+    // exchange of (largest logit, its index) per row of a vocabulary-parallel head: a second small
+    // inbox [2][world][2 * AB2_TP_ARGMAX_ROWS] words at this word offset of every rank's block
+    unsigned long long argmax_off;
+    uint32_t *argmax_epoch, *argmax_done;
 };
+constexpr int AB2_TP_ARGMAX_ROWS = 64;
 
 __device__ __forceinline__ unsigned long long tp_ll_pack(float v, uint32_t exchange) {
     return (unsigned long long)__float_as_uint(v) | ((unsigned long long)exchange << 32);
@@ -86,4 +91,8 @@ bool tp_peer_ready(const ab2_tp *tp, size_t count);
 int tp_peer_reduce_add(ab2_tp *tp, void *x_bf16, size_t count, cudaStream_t s);
 // This rank's `count` f32 partial sums of the current exchange into every rank's inbox.
 int tp_peer_deposit(ab2_tp *tp, const float *partial_f32, size_t count, cudaStream_t s);
+// out[row] = index (in the whole vocabulary) of the last maximum of the row's logits, whose shard
+// [rows][vn] this rank holds: local argmax, one (value, index) pair per rank through the peer
+// exchange, the same choice on every rank.  rows <= AB2_TP_ARGMAX_ROWS.
+int tp_peer_argmax(ab2_tp *tp, const void *logits_local, int rows, int vn, ab2_dtype dtype, uint32_t *out, cudaStream_t s);
 }
