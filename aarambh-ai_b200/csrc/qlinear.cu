@@ -227,7 +227,17 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     // weights are latency-bound, and fewer, longer ranges keep most cut tiles inside
     // one CTA (finished through shared memory).
     const long long total = (long long)tiles * (w->K / 128);
-    const int grid = (int)std::min<long long>(sc.max_ctas, std::max<long long>(1, (total / 8 + W4W_WARPS - 1) / W4W_WARPS));
+    // Small weights are latency-bound: what a launch costs is the serial work of one warp plus the
+    // finishing of cut tiles.  One 16-row tile per CTA (G / 8 blocks per warp) keeps every cut inside a
+    // CTA (finished through shared memory; a tile cut between CTAs goes through partial sums and a
+    // counter in L2) and halves the blocks a warp walks: taken whenever it fits the resident CTAs and
+    // leaves a warp at least 4 blocks (the Large block's qkv, o and down projections: 557 -> 592 tok/s).
+    // Large weights keep equal ranges over every resident CTA: for them balance across SMs matters more
+    // (one tile set per CTA on the gate|up weight: 488 tok/s).
+    static const bool align_off = getenv("AB2_GEMV_ALIGN") != nullptr && atoi(getenv("AB2_GEMV_ALIGN")) == 0;
+    const int G = w->K / 128;
+    int grid = (int)std::min<long long>(sc.max_ctas, std::max<long long>(1, (total / 8 + W4W_WARPS - 1) / W4W_WARPS));
+    if (!align_off && G % W4W_WARPS == 0 && G / W4W_WARPS >= 4 && tiles <= sc.max_ctas) grid = tiles;
     const uint32_t *wt = (const uint32_t *)w->codes;
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     // 17..64 tokens: the tensor-memory decode GEMM, 32 tokens per pass (the codes are unpacked once
