@@ -141,6 +141,16 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
         to_fetch -= W4M1_COPY_BLOCKS;
     }
 
+    // the norm weights are constant too, and a step's weight stream has long evicted them from L2:
+    // request them now so that the prologue does not wait for DRAM
+    if (NORM) {
+#pragma unroll
+        for (int it = 0; it < NV; ++it) {
+            const int i = threadIdx.x + it * 256;
+            if (i < (K >> 3)) asm volatile("prefetch.global.L1 [%0];\n" ::"l"(norm_w + 8 * i));
+        }
+    }
+
     // activations (and the residual) come from the preceding kernel
     pdl_wait();
     pdl_launch_dependents();
