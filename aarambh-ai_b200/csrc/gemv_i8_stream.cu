@@ -27,12 +27,14 @@ int device_sm_count();
 namespace {
 
 constexpr int I8S_WARPS = 8;
-constexpr int I8S_UNROLL = 4;   // chunks in flight per warp (8 costs occupancy: 0.38 against 0.59 of HBM on 4096 x 14336)
+// Chunks in flight per warp are a template argument: 4 for K up to 8192 (6 gives 0.51 against 0.59 of
+// HBM on 4096 x 14336, 8 gives 0.38: registers cost occupancy), 6 for longer rows (0.56 against 0.49 on
+// 14336 x 4096: more iterations per warp to overlap).
 
 template <typename T>
 __device__ __forceinline__ void store_out(T *y, size_t i, float v) { y[i] = from_f32<T>(v); }
 
-template <int RT>  // 16-row tiles per CTA (the activation fragments of a chunk serve all of them)
+template <int RT, int I8S_UNROLL>  // RT: 16-row tiles per CTA (the activation fragments of a chunk serve all of them)
 __global__ void __launch_bounds__(256)
 gemv_i8_stream_kernel(const int8_t *__restrict__ codes, const float *__restrict__ scales,
                       const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y, int N, int K, int M) {
@@ -187,8 +189,9 @@ int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaS
     AB2_CUDA(cudaGetDevice(&dev));
     AB2_REQUIRE(dev >= 0 && dev < 64, AB2_ERR_BAD_ARG, "device index %d out of range", dev);
     if (!configured[dev]) {
-        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<1, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        AB2_CUDA(cudaFuncSetAttribute(gemv_i8_stream_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         configured[dev] = true;
     }
     // two 16-row tiles per CTA once that still leaves every SM a few CTAs (the activations are staged per CTA)
@@ -196,10 +199,18 @@ int qlinear_i8_stream(const ab2_qweight *w, const void *x, int M, void *y, cudaS
     // measured: two tiles per CTA are slower up to 4 tokens (one token: 0.47 against 0.59 of HBM on
     // 4096 x 14336) and faster at 8, where staging the activations per CTA weighs most (32.7 against 44.7 us)
     const bool two = M >= 8;
-    cudaError_t e = two ? launch_kernel(gemv_i8_stream_kernel<2>, dim3((tiles + 1) / 2), dim3(256), smem, s, (const int8_t *)w->codes,
-                                        (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M)
-                        : launch_kernel(gemv_i8_stream_kernel<1>, dim3(tiles), dim3(256), smem, s, (const int8_t *)w->codes,
-                                        (const float *)w->scales, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
+    const int8_t *codes = (const int8_t *)w->codes;
+    const float *scales = (const float *)w->scales;
+    cudaError_t e;
+    if (two)
+        e = launch_kernel(gemv_i8_stream_kernel<2, 4>, dim3((tiles + 1) / 2), dim3(256), smem, s, codes, scales,
+                          (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
+    else if (w->K > 8192)
+        e = launch_kernel(gemv_i8_stream_kernel<1, 6>, dim3(tiles), dim3(256), smem, s, codes, scales,
+                          (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
+    else
+        e = launch_kernel(gemv_i8_stream_kernel<1, 4>, dim3(tiles), dim3(256), smem, s, codes, scales,
+                          (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, w->N, w->K, M);
     if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "INT8 GEMV launch failed: %s", cudaGetErrorString(e));
     return AB2_OK;
 }
