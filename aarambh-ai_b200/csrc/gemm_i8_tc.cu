@@ -305,7 +305,7 @@ bool qlinear_i8_tc_eligible(const ab2_qweight *w, ab2_dtype dtype, int M) {
 // Y[M][N] = X[M][K] . W^T on the tcgen05 path (INT8 codes, f32 scale per channel, bf16 activations).
 int qlinear_i8_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
     AB2_REQUIRE(((uintptr_t)x & 15) == 0, AB2_ERR_BAD_ALIGN, "activations must be 16-byte aligned");
-    if (M <= 1024) return launch_i8_tc<128>(w, x, M, y, s);
+    if (M <= 256) return launch_i8_tc<128>(w, x, M, y, s);  // as for the W4A16 GEMM: 256-token tiles from 257 tokens on
     return launch_i8_tc<256>(w, x, M, y, s);
 }
 

@@ -285,7 +285,10 @@ int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t 
 int qlinear_w4a16_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
     AB2_REQUIRE(((uintptr_t)x & 15) == 0 && (w->K * 2) % 16 == 0, AB2_ERR_BAD_ALIGN, "activations must be 16-byte aligned");
     if (M <= 48) return launch_tc<32>(w, x, M, y, s);
-    if (M <= 1024) return launch_tc<128>(w, x, M, y, s);
+    // From 257 tokens on, 256-token tiles: an unpacked weight stage then feeds twice the MMA work, which
+    // is what bounds the kernel at 128 (512 tokens on the 4096 x 28672 weight: 139 against 228 us), even
+    // where fewer tiles than SMs remain (4096 x 4096 at 512 tokens: 45 against 43 us).
+    if (M <= 256) return launch_tc<128>(w, x, M, y, s);
     return launch_tc<256>(w, x, M, y, s);
 }
 
