@@ -67,7 +67,7 @@ __host__ __device__ constexpr int tc_xstages() {
 template <int NTOK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CUtensorMap xmap,
-                     __nv_bfloat16 *__restrict__ y, int N, int K, int M, int *status) {
+                     __nv_bfloat16 *__restrict__ y, int N, int K, int M, int *status, int ksplit, float *part) {
     constexpr int B_BYTES = NTOK * 128;
     constexpr int XST = tc_xstages<NTOK>();
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) | ((128u >> 4) << 24);
@@ -81,7 +81,14 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = K >> 7, tiles16 = (N + 15) >> 4;
     const int n_tiles = (N + 127) >> 7, m_tiles = (M + NTOK - 1) / NTOK;
-    const int items = n_tiles * m_tiles;
+    // an item is (channel tile, token tile, K split): with fewer tiles than SMs the groups of a tile are
+    // divided over `ksplit` CTAs, which leave f32 partial sums in `part` [ksplit][M][N] for a reduce pass
+    const int items = n_tiles * m_tiles * ksplit;
+#define TC_ITEM(it)                                                                    \
+    const int ksp = (it) % ksplit, tile_ = (it) / ksplit;                              \
+    const int nt = tile_ / m_tiles, mt = tile_ % m_tiles;                              \
+    const int g0 = (int)((long long)ksp * G / ksplit), g1 = (int)((long long)(ksp + 1) * G / ksplit); \
+    (void)ksp; (void)nt; (void)mt; (void)g0; (void)g1;
     volatile int *failed = &sh->failed;
 
     if (threadIdx.x == 0) {
@@ -108,9 +115,9 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         // copies of a group leave in parallel instead of one after the other from a single thread.
         uint32_t wuse = 0;
         for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
-            const int nt = it / m_tiles;
+            TC_ITEM(it)
             const int nblk = min(8, tiles16 - nt * 8);
-            for (int g = 0; g < G && !*failed; ++g, ++wuse) {
+            for (int g = g0; g < g1 && !*failed; ++g, ++wuse) {
                 const int ws = wuse % TC_WSLOTS;
                 int ok = 1;
                 if (lane == 0) {
@@ -129,8 +136,8 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         if (lane == 0) {
             uint32_t suse = 0;
             for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
-                const int mt = it % m_tiles;
-                for (int ks = 0; ks < 2 * G && !*failed; ++ks, ++suse) {
+                TC_ITEM(it)
+                for (int ks = 2 * g0; ks < 2 * g1 && !*failed; ++ks, ++suse) {
                     const int xs = suse % XST;
                     // rings of equal depth share one "stage free" barrier (one commit per stage instead of two)
                     if (!bar_wait(XST == TC_STAGES ? &sh->sempty[xs] : &sh->xempty[xs], ((suse / XST) & 1) ^ 1, failed)) break;
@@ -147,7 +154,8 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             if (!bar_wait(&sh->accempty[ab], ((tuse >> 1) & 1) ^ 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const uint32_t tacc = tmem + (uint32_t)(ab * NTOK);
-            for (int ks = 0; ks < 2 * G && !*failed; ++ks, ++suse) {
+            TC_ITEM(it)
+            for (int ks = 2 * g0; ks < 2 * g1 && !*failed; ++ks, ++suse) {
                 const int s = suse % TC_STAGES, xs = suse % XST;
                 if (!bar_wait(&sh->xfull[xs], (suse / XST) & 1, failed)) break;
                 if (!bar_wait(&sh->afull[s], (suse / TC_STAGES) & 1, failed)) break;
@@ -156,7 +164,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                     const uint32_t a0 = sptr(a_st + s * TC_A_BYTES), b0 = sptr(b_st + xs * B_BYTES);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tacc, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, (ks | k) != 0);
+                        umma_bf16(tacc, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), IDESC, ((ks - 2 * g0) | k) != 0);
                     umma_commit(&sh->sempty[s]);  // the operand stages are free when the MMAs retire
                     if (XST != TC_STAGES) umma_commit(&sh->xempty[xs]);
                 }
@@ -173,7 +181,8 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         uint32_t k_mask = 0x000F000Fu, k_magic = 0x43004300u;
         asm volatile("" : "+r"(k_mask), "+r"(k_magic));
         for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x) {
-            for (int g = 0; g < G && !*failed; ++g, ++wuse) {
+            TC_ITEM(it)
+            for (int g = g0; g < g1 && !*failed; ++g, ++wuse) {
                 const int ws = wuse % TC_WSLOTS;
                 if (!bar_wait(&sh->wfull[ws], (wuse / TC_WSLOTS) & 1, failed)) break;
                 const uint32_t *bw = (const uint32_t *)(w_ring + ws * TC_WSLOT_BYTES) + blk * TC_BLOCK_WORDS;
@@ -213,7 +222,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         const int quad = warp & 3;
         uint32_t tuse = 0;
         for (int it = blockIdx.x; it < items && !*failed; it += gridDim.x, ++tuse) {
-            const int nt = it / m_tiles, mt = it % m_tiles;
+            TC_ITEM(it)
             const int ab = tuse & 1;
             if (!bar_wait(&sh->accfull[ab], (tuse >> 1) & 1, failed)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -235,7 +244,10 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int tok = mt * NTOK + c * 32 + j;
-                        if (tok < M) y[(size_t)tok * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        if (tok < M) {
+                            if (ksplit > 1) part[((size_t)ksp * M + tok) * N + n] = __uint_as_float(v[j]);
+                            else y[(size_t)tok * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        }
                     }
                 }
             }
@@ -255,6 +267,43 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
     }
 }
 
+// y[i] = bf16(sum over splits of part[s][i]): eight elements per thread
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, __nv_bfloat16 *__restrict__ y, size_t n8, size_t stride, int ksplit) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < ksplit; ++s) {
+        const float4 a = reinterpret_cast<const float4 *>(part + s * stride)[2 * i];
+        const float4 b = reinterpret_cast<const float4 *>(part + s * stride)[2 * i + 1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        o[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * j])) |
+               ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * j + 1])) << 16);
+    reinterpret_cast<uint4 *>(y)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Workspace of the K split, one per device, grown on demand (prefill passes are not captured in graphs;
+// a capture in progress simply runs without the split).
+constexpr size_t TC_SPLIT_MAX_BYTES = (size_t)128 << 20;
+static float *g_split_ws[64] = {nullptr};
+static size_t g_split_bytes[64] = {0};
+static float *split_workspace(int dev, size_t bytes, cudaStream_t s) {
+    if (g_split_bytes[dev] >= bytes) return g_split_ws[dev];
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    if (cudaDeviceSynchronize() != cudaSuccess) return nullptr;
+    if (g_split_ws[dev]) cudaFree(g_split_ws[dev]);
+    g_split_ws[dev] = nullptr;
+    g_split_bytes[dev] = 0;
+    if (cudaMalloc((void **)&g_split_ws[dev], bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    g_split_bytes[dev] = bytes;
+    return g_split_ws[dev];
+}
+
 template <int NTOK>
 int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t s) {
     int *status = nullptr;
@@ -272,10 +321,28 @@ int launch_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStream_t 
         AB2_CUDA(cudaFuncSetAttribute(gemm_w4a16_tc_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[dev] = true;
     }
-    const int items = ((w->N + 127) / 128) * ((M + NTOK - 1) / NTOK);
-    const int grid = std::min(items, device_sm_count());
-    gemm_w4a16_tc_kernel<NTOK><<<grid, TC_THREADS, smem, s>>>((const uint32_t *)w->codes, map, (__nv_bfloat16 *)y, w->N, w->K, M, status);
+    const int tiles = ((w->N + 127) / 128) * ((M + NTOK - 1) / NTOK);
+    // Fewer tiles than about half the SMs: split K so that the machine is busy (512 tokens on the
+    // 14336 x 4096 weight are 64 tiles of 256 tokens).  The sums of the splits are f32; one rounding.
+    const int sms = device_sm_count(), G = w->K / 128;
+    int ksplit = 1;
+    float *part = nullptr;
+    static const bool no_split = getenv("AB2_GEMM_NO_SPLITK") != nullptr;
+    if (!no_split && tiles * 2 <= sms + sms / 4 && G >= 8 && w->N % 8 == 0) {
+        ksplit = std::max(1, std::min(4, std::min(G / 4, sms / tiles)));  // all items in one wave
+        const size_t bytes = (size_t)ksplit * M * w->N * sizeof(float);
+        part = ksplit > 1 && bytes <= TC_SPLIT_MAX_BYTES ? split_workspace(dev, bytes, s) : nullptr;
+        if (!part) ksplit = 1;
+    }
+    const int items = tiles * ksplit;
+    const int grid = std::min(items, sms);
+    gemm_w4a16_tc_kernel<NTOK><<<grid, TC_THREADS, smem, s>>>((const uint32_t *)w->codes, map, (__nv_bfloat16 *)y, w->N, w->K, M, status, ksplit, part);
     AB2_LAUNCH_CHECK();
+    if (ksplit > 1) {
+        const size_t n8 = (size_t)M * w->N / 8;
+        splitk_reduce_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(part, (__nv_bfloat16 *)y, n8, (size_t)M * w->N, ksplit);
+        AB2_LAUNCH_CHECK();
+    }
     return AB2_OK;
 }
 
