@@ -57,7 +57,7 @@ constexpr int DG_WSLOTS = 12;        // depth of a packed-weight ring (two block
 constexpr int DG_WSLOT_BYTES = 2 * W4_BLOCK_WORDS * 4;  // per ring; four rings (one per 32 channels) = ~100 KB in flight per SM
 constexpr int DG_A_BYTES = 128 * 128;  // 128 channels x 64 bf16
 constexpr int DG_MMA_WARPS = 2;        // MMA-issue warps, taking alternate units (warp 1 and the warps after the epilogue)
-constexpr int DG_THREADS = 448 + 32 * (DG_MMA_WARPS - 1);
+constexpr int DG_THREADS = 448 + 32 * (DG_MMA_WARPS - 1) + 32;  // the last warp fetches the packed weights
 constexpr int DG_ACC = 4;             // accumulator pairs (D, S) in tensor memory
 // An MMA-issue warp must see every phase of the barriers it waits on (a parity wait cannot tell
 // phase k from phase k + 2), so the stages, activation stages and accumulators a unit uses must come
@@ -136,7 +136,7 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int q = 0; q < 4; ++q)
-            for (int i = 0; i < DG_WSLOTS; ++i) { bar_init(&sh->wfull[q][i], 2); bar_init(&sh->wempty[q][i], 2); }
+            for (int i = 0; i < DG_WSLOTS; ++i) { bar_init(&sh->wfull[q][i], 1); bar_init(&sh->wempty[q][i], 2); }
         for (int i = 0; i < DG_STAGES; ++i) { bar_init(&sh->afull[i], 4); bar_init(&sh->sempty[i], 1); }
         for (int i = 0; i < DG_XSTAGES; ++i) { bar_init(&sh->xfull[i], 1); bar_init(&sh->xempty[i], 1); }
         for (int i = 0; i < DG_ACC; ++i) { bar_init(&sh->accfull[i], 1); bar_init(&sh->accempty[i], 4); }
@@ -169,6 +169,29 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
                 }
             }
         }
+    } else if (warp == DG_THREADS / 32 - 1) {
+        // ---------------------------------------------------------- producer of the packed weights
+        // Lane b fetches block b of a unit (blocks 2q and 2q + 1 go to ring q); issuing a copy occupies a
+        // warp for a few hundred cycles, which the unpack warps used to pay once per unit each.
+        const int n_units = rg.u1 - rg.u0;
+        for (int use = 0; use < n_units && !*failed; ++use) {
+            const int u = rg.u0 + use, nt = u / G, g = u - nt * G, ws = use % DG_WSLOTS;
+            int ok = 1;
+            if (use >= DG_WSLOTS && lane < 4) ok = bar_wait(&sh->wempty[lane][ws], ((use / DG_WSLOTS) & 1) ^ 1, failed) ? 1 : 0;
+            if (!__all_sync(0xffffffffu, ok)) break;
+            if (lane < 8) {
+                const int q = lane >> 1, blk = nt * 8 + lane;
+                if ((lane & 1) == 0) {
+                    const int have = (blk < tiles16 ? 1 : 0) + (blk + 1 < tiles16 ? 1 : 0);
+                    if (have) bar_expect_tx(&sh->wfull[q][ws], (uint32_t)have * W4_BLOCK_WORDS * 4);
+                    else bar_arrive(&sh->wfull[q][ws]);  // a channel tile past the last row has fewer blocks
+                }
+            }
+            __syncwarp();
+            if (lane < 8 && nt * 8 + lane < tiles16)
+                bulk_copy(w_ring + (lane >> 1) * DG_WSLOTS * DG_WSLOT_BYTES + ws * DG_WSLOT_BYTES + (lane & 1) * W4_BLOCK_WORDS * 4,
+                          wt + ((size_t)(nt * 8 + lane) * G + g) * W4_BLOCK_WORDS, W4_BLOCK_WORDS * 4, &sh->wfull[lane >> 1][ws]);
+        }
     } else if (warp == 1 || warp >= 14) {
         // ---------------------------------------------------------- MMA issue (alternate units per warp)
         const uint32_t my_id = warp == 1 ? 0u : (uint32_t)(warp - 13);
@@ -200,32 +223,15 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
         }
     } else if (warp < 10) {
         // ---------------------------------------------------------- unpack: codes -> bf16 128 + q
-        // The two warps that share 32 channels (one per half of the group) also fetch those
-        // channels' packed blocks themselves, one block each, into a ring of their own: eight
-        // lanes issue the bulk copies of a unit in parallel, and the weights, being constant,
-        // start streaming before the preceding kernel has finished.
+        // The two warps that share 32 channels (one per half of the group) read those channels'
+        // two packed blocks from a ring of their own, filled by the producer warp.
         const int t = (threadIdx.x - 64) & 127;   // channel within the 128-channel tile
         const int half = (threadIdx.x - 64) >> 7;  // which 64 of the group's 128 K-elements
         const int q = t >> 5;                      // ring: channels 32q .. 32q+31 = blocks 2q, 2q+1
         const int blk = t >> 4, r = t & 15;
-        const int my_block = 2 * q + half;         // the block this warp's lane 0 fetches
         uint8_t *ring = w_ring + q * DG_WSLOTS * DG_WSLOT_BYTES;
         uint32_t k_mask = 0x000F000Fu, k_magic = 0x43004300u;
         asm volatile("" : "+r"(k_mask), "+r"(k_magic));
-        auto fetch = [&](int u, uint32_t fuse) {   // lane 0: block my_block of unit u into slot fuse % DG_WSLOTS
-            const int nt = u / G, g = u - nt * G;
-            const int ws = fuse % DG_WSLOTS;
-            if (nt * 8 + my_block < tiles16) {
-                bar_expect_tx(&sh->wfull[q][ws], W4_BLOCK_WORDS * 4);
-                bulk_copy(ring + ws * DG_WSLOT_BYTES + half * W4_BLOCK_WORDS * 4,
-                          wt + ((size_t)(nt * 8 + my_block) * G + g) * W4_BLOCK_WORDS, W4_BLOCK_WORDS * 4, &sh->wfull[q][ws]);
-            } else {
-                bar_arrive(&sh->wfull[q][ws]);  // a channel tile past the last row has fewer blocks
-            }
-        };
-        const int n_units = rg.u1 - rg.u0;
-        if (lane == 0)
-            for (int i = 0; i < min(DG_WSLOTS, n_units); ++i) fetch(rg.u0 + i, (uint32_t)i);
         uint32_t use = 0;
         for (int u = rg.u0; u < rg.u1 && !*failed; ++u, ++use) {
             const int ws = use % DG_WSLOTS;
@@ -239,14 +245,6 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             // one arrival per warp: arrivals on one mbarrier serialise on its word
             __syncwarp();
             if (lane == 0) bar_arrive(&sh->wempty[q][ws]);
-            // refill the slot released one unit ago (both warps of the pair have read it by now, or will shortly)
-            if (lane == 0 && use >= 1 && (int)use - 1 + DG_WSLOTS < n_units) {
-                const uint32_t pu = use - 1;
-                // on a time-out `failed` is set and every lane leaves at its next wait
-                if (bar_wait(&sh->wempty[q][pu % DG_WSLOTS], (pu / DG_WSLOTS) & 1, failed))
-                    fetch(rg.u0 + (int)pu + DG_WSLOTS, pu + DG_WSLOTS);
-            }
-            __syncwarp();
             const uint32_t suse = 2 * use + half;
             const int s = suse % DG_STAGES;
             if (!bar_wait(&sh->sempty[s], ((suse / DG_STAGES) & 1) ^ 1, failed)) break;
