@@ -27,13 +27,16 @@
 // order.  One CTA per SM, warp-specialised:
 //   warp 0        TMA tile loads of X (two 64-wide halves per group, 128-byte
 //                 swizzle) into the operand-B stages
-//   warp 1        tensor-memory allocation, tcgen05.mma issue, commits
-//   warps 2-9     unpack: thread = (channel, half of the group); each warp also
-//                 fetches one 16-channel packed block per unit by a bulk copy
-//                 into the ring it shares with its partner warp (a single thread
-//                 issuing all eight copies of a unit bounds the kernel)
-//   warps 10-13   epilogue: tcgen05.ld of D and S, scale / zero point, running
-//                 sums, the tile's final store (or partial + hand-over)
+//   warps 1, 14   tcgen05.mma issue and commits on alternate units (warp 1 also
+//                 allocates the tensor memory)
+//   warps 2-9     unpack: thread = (channel, half of the group), reading the 32
+//                 channels' two packed blocks from the ring the warp shares with
+//                 its partner warp
+//   warps 10-13   epilogue: tcgen05.ld of D, scale, running sums, the tile's final
+//                 store (or partial + hand-over)
+//   warp 15       packed weights: lane b copies block b of a unit into the rings
+//                 (eight bulk copies in parallel; issuing one keeps a warp busy for
+//                 a few hundred cycles, which the unpack warps cannot afford)
 // Every wait on an mbarrier is bounded; on a time-out the CTA records
 // AB2_ERR_TIMEOUT, stops issuing work, still frees its tensor memory and returns.
 #include <algorithm>
