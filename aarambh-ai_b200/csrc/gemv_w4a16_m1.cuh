@@ -333,7 +333,8 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     const int cta_tile0 = (cta_w0 * base + min(cta_w0, rem)) / G;
 
     int tile = b0 / G, g = b0 - tile * G;
-    uint32_t cur = ring0, bar = bar0, parity = 0, second = 0;  // second: the stage's second block is next
+    // cur: the stage of the next block; second: its first block has been consumed already
+    uint32_t cur = ring0, bar = bar0, parity = 0, second = 0;
     const uint32_t ring_end = ring0 + STAGES * STAGE_BYTES;
     uint4 xw[4];
 #pragma unroll
@@ -345,14 +346,11 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
         float acc_a = 0.f, acc_b = 0.f;  // rows r and r + 8 of the tile, token 0 (lanes c == 0)
         uint32_t xaddr = xlane + g * 256, gaddr = gs0 + g * 8;
 
-        for (int it = 0; it < n; ++it) {
-            if (!second && !mbar_wait_addr(bar, parity)) {
-                if (lane == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
-                return;
-            }
-            const uint4 wa = lds128(cur + code_off);
-            const uint4 wb = lds128(cur + code_off + 512);
-            const uint32_t pa = lds32(cur + param_off), pb = lds32(cur + param_off + 32);
+        // one block at `addr` of the ring: unpack, 8 MMAs, the group's scale and zero point
+        auto block = [&](uint32_t addr) {
+            const uint4 wa = lds128(addr + code_off);
+            const uint4 wb = lds128(addr + code_off + 512);
+            const uint32_t pa = lds32(addr + param_off), pb = lds32(addr + param_off + 32);
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) lds128_if(has_x, xaddr + wi * 16, xw[wi]);
             float C2, T;
@@ -385,20 +383,41 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
             const float nza = __uint_as_float(pa & 0xffff0000u), nzb = __uint_as_float(pb & 0xffff0000u);
             acc_a = fmaf(sa, (d[0] + d2[0]) - fmaf(-nza, T, C2), acc_a);
             acc_b = fmaf(sb, (d[2] + d2[2]) - fmaf(-nzb, T, C2), acc_b);
-
-            // After its second block, refill the stage with the two blocks STAGES stages ahead:
-            // every lane's loads of it were issued at the top of the steps and have been consumed.
-            cur += BLOCK_BYTES;
-            if (second) {
-                __syncwarp();
-                bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur - STAGE_BYTES, src,
-                            (uint32_t)min(to_fetch, W4M1_COPY_BLOCKS) * BLOCK_BYTES, bar);
-                src += W4M1_COPY_BLOCKS * W4_BLOCK_WORDS;
-                to_fetch -= W4M1_COPY_BLOCKS;
-                bar += 8;
-                if (cur == ring_end) { cur = ring0; bar = bar0; parity ^= 1; }
+        };
+        // The stage `cur` points into has been consumed: refill it with the two blocks STAGES stages
+        // ahead (every lane's loads of it were issued above and have been consumed) and move on.
+        auto next_stage = [&]() {
+            __syncwarp();
+            bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur, src, (uint32_t)min(to_fetch, W4M1_COPY_BLOCKS) * BLOCK_BYTES, bar);
+            src += W4M1_COPY_BLOCKS * W4_BLOCK_WORDS;
+            to_fetch -= W4M1_COPY_BLOCKS;
+            cur += STAGE_BYTES;
+            bar += 8;
+            if (cur == ring_end) { cur = ring0; bar = bar0; parity ^= 1; }
+        };
+        int it = 0;
+        if (second) {  // the tile starts at the second block of a stage whose first block closed the previous tile
+            block(cur + BLOCK_BYTES);
+            next_stage();
+            second = 0;
+            it = 1;
+        }
+        for (; it + 2 <= n; it += 2) {  // whole stages: one wait, two blocks, one refill
+            if (!mbar_wait_addr(bar, parity)) {
+                if (lane == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+                return;
             }
-            second ^= 1u;
+#pragma unroll 1
+            for (uint32_t h = 0; h < W4M1_COPY_BLOCKS * BLOCK_BYTES; h += BLOCK_BYTES) block(cur + h);
+            next_stage();
+        }
+        if (it < n) {  // the tile (or the range) ends on the first block of a stage
+            if (!mbar_wait_addr(bar, parity)) {
+                if (lane == 0) atomicExch(status, (int)AB2_ERR_TIMEOUT);
+                return;
+            }
+            block(cur);
+            second = 1;
         }
         b += n;
 
