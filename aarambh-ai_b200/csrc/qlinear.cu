@@ -10,6 +10,7 @@
 #include "gemv_w4a16_mma.cuh"
 #include "gemv_w4a16_warp.cuh"
 #include "gemv_w4a16_m1.cuh"
+#include "gemv_w4a16_strip.cuh"
 
 using namespace ab2;
 
@@ -141,7 +142,9 @@ static int gemv_scratch_for(cudaStream_t s, GemvScratch *out) {
                         "on the stream before capturing (its scratch buffers are allocated then)");
         GemvScratch sc;
         sc.max_ctas = device_sm_count() * 3;
-        const size_t pbytes = (size_t)sc.max_ctas * W4W_WARPS * 2 * W4W_SLOT_FLOATS * sizeof(float);
+        // two partial tiles per warp of the warp kernels, or two partial tile sets per CTA of the strip kernel
+        const size_t pbytes = std::max((size_t)sc.max_ctas * W4W_WARPS * 2 * W4W_SLOT_FLOATS,
+                                       (size_t)device_sm_count() * 2 * W4S_MAX_SLOT_FLOATS) * sizeof(float);
         AB2_CUDA(cudaMalloc((void **)&sc.partials, pbytes));
         AB2_CUDA(cudaMalloc((void **)&sc.counters, W4W_MAX_TILES * sizeof(int)));
         AB2_CUDA(cudaMemset(sc.counters, 0, W4W_MAX_TILES * sizeof(int)));
@@ -204,6 +207,29 @@ static cudaError_t launch_w4a16_m1(const ab2_qweight *w, const __nv_bfloat16 *x,
     return launch_w4a16_m1_inst<EPI, 2, 8, false>(w, x, norm_w, eps, y, resid, grid, sc, status, s);
 }
 
+// 9..32 tokens: the register-tiled strip kernel (gemv_w4a16_strip.cuh), one CTA per SM.
+template <class S, int EPI>
+static cudaError_t launch_w4a16_strip(const ab2_qweight *w, const __nv_bfloat16 *x, int M, __nv_bfloat16 *y,
+                                      const __nv_bfloat16 *resid, const GemvScratch &sc, int *status,
+                                      cudaStream_t s) {
+    static_assert(S::SLOT_FLOATS <= W4S_MAX_SLOT_FLOATS, "the scratch holds two partial tile sets per CTA");
+    static_assert(S::SMEM <= 227 * 1024, "shared memory of a CTA");
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_w4a16_strip_kernel<S, EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    const int tiles = (w->N + 15) / 16, sets = (tiles + S::WS * S::RT - 1) / (S::WS * S::RT);
+    const long long total = (long long)sets * (w->K / 128);
+    const int grid = (int)std::min<long long>(device_sm_count(), total);
+    return launch_kernel(gemv_w4a16_strip_kernel<S, EPI>, dim3(grid), dim3(S::WARPS * 32), S::SMEM, s,
+                         (const uint32_t *)w->codes, x, y, resid, w->N, w->K, M, sc.partials, sc.counters, status);
+}
+
 constexpr int W4M1_MAX_K = 16384;
 constexpr int W4M1_PLAIN_MAX_K = 8192;
 
@@ -244,17 +270,57 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     // per pass whatever the token count; the warp kernel re-reads its activations for every block
     // and needs a pass per 16 tokens).  Measured on the largest shape: 343 us per pass against
     // 155 us per 16-token pass of the warp kernel, so it pays from 17 tokens.
-    constexpr int tc_min_m = 17;
-    if (M >= tc_min_m && EPI != W4_EPI_F32_PEER && !norm_w && w->N % 16 == 0) {
-        for (int m0 = 0; m0 < M; m0 += 32) {
-            const int mv = std::min(32, M - m0);
-            const char *xp = (const char *)x + (size_t)m0 * w->K * 2;
-            char *yp = (char *)y + (size_t)m0 * out_n * (EPI == W4_EPI_F32 ? 4 : 2);
-            const char *rp = resid ? (const char *)resid + (size_t)m0 * out_n * 2 : nullptr;
-            rc = qlinear_w4a16_tc_decode(w, xp, mv, yp, rp, EPI, sc.partials, sc.counters, sc.max_ctas, s);
-            if (rc != AB2_OK) return rc;
+    // More than 8 tokens go in chunks of up to 32:
+    //   9..24 tokens (and 25..32 on a weight of 32768 rows or more): the strip kernel - a warp multiplies
+    //     64 or 32 rows by all tokens, so the activations it loads serve several weight blocks and the
+    //     codes are unpacked once for every token.  On the largest shape it takes 96 / 113 / 150 us for
+    //     16 / 24 / 32 tokens; the warp kernel needs 155 us per 16 tokens.
+    //   25..32 tokens on the layer shapes: the tensor-memory decode GEMM, whose pass costs the same
+    //     whatever the token count (170 us on the largest shape, 15 / 26 / 27 us on 4096 x 4096,
+    //     4096 x 14336, 14336 x 4096 against the strip kernel's 17 / 29 / 30 us).
+    static const bool strip_off = getenv("AB2_GEMV_NO_STRIP") != nullptr;
+    if constexpr (EPI != W4_EPI_F32_PEER) {
+        if (M >= 9 && !norm_w) {
+            const bool tc_ok = w->N % 16 == 0;
+            // equal chunks, in whole token tiles: 40 tokens go as 24 + 16, not as 32 + 8
+            const int nchunks = (M + 31) / 32, chunk = ((M + nchunks - 1) / nchunks + 7) / 8 * 8;
+            for (int m0 = 0; m0 < M; m0 += chunk) {
+                const int mv = std::min(chunk, M - m0);
+                const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;
+                __nv_bfloat16 *yp = EPI == W4_EPI_F32 ? (__nv_bfloat16 *)((float *)y + (size_t)m0 * out_n)
+                                                      : (__nv_bfloat16 *)y + (size_t)m0 * out_n;
+                const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
+                if (!strip_off && mv >= 9 && (mv <= 24 || w->N >= 32768 || !tc_ok)) {
+                    cudaError_t e;
+                    // token tiles, tiles per strip, strips x K slices of a CTA
+                    switch ((mv + 7) / 8) {
+                    case 2: e = launch_w4a16_strip<W4sShape<2, 2, 8, 2>, EPI>(w, xp, mv, yp, rp, sc, status, s); break;
+                    case 3: e = launch_w4a16_strip<W4sShape<3, 4, 4, 2>, EPI>(w, xp, mv, yp, rp, sc, status, s); break;
+                    default: e = launch_w4a16_strip<W4sShape<4, 4, 4, 2>, EPI>(w, xp, mv, yp, rp, sc, status, s); break;
+                    }
+                    if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "GEMV launch failed: %s", cudaGetErrorString(e));
+                } else if (tc_ok && mv >= 17) {
+                    rc = qlinear_w4a16_tc_decode(w, xp, mv, yp, rp, EPI, sc.partials, sc.counters, sc.max_ctas, s);
+                    if (rc != AB2_OK) return rc;
+                } else {
+                    for (int m1 = 0; m1 < mv; m1 += 16) {
+                        const int mw = std::min(16, mv - m1);
+                        const __nv_bfloat16 *xq = xp + (size_t)m1 * w->K;
+                        __nv_bfloat16 *yq = EPI == W4_EPI_F32 ? (__nv_bfloat16 *)((float *)yp + (size_t)m1 * out_n)
+                                                              : yp + (size_t)m1 * out_n;
+                        const __nv_bfloat16 *rq = rp ? rp + (size_t)m1 * out_n : nullptr;
+                        cudaError_t e =
+                            mw > 8 ? launch_kernel(gemv_w4a16_warp_kernel<2, EPI>, dim3(grid), dim3(256), 0, s, wt, xq, yq,
+                                                   rq, w->N, w->K, mw, sc.partials, sc.counters, status)
+                                   : launch_kernel(gemv_w4a16_warp_kernel<1, EPI>, dim3(grid), dim3(256), 0, s, wt, xq, yq,
+                                                   rq, w->N, w->K, mw, sc.partials, sc.counters, status);
+                        if (e != cudaSuccess) return fail(AB2_ERR_CUDA, "GEMV launch failed: %s", cudaGetErrorString(e));
+                    }
+                }
+            }
+            AB2_LAUNCH_CHECK();
+            return AB2_OK;
         }
-        return AB2_OK;
     }
     for (int m0 = 0; m0 < M; m0 += 16) {
         const __nv_bfloat16 *xp = (const __nv_bfloat16 *)x + (size_t)m0 * w->K;

@@ -78,6 +78,17 @@ def time_graph(fn, reps, stream):
     return a.elapsed_time(b) * 1e-3 / reps
 
 
+def w4a16_kernel_name(M, N):
+    """The kernel the library's dispatch takes for M tokens on a W4A16 weight of N rows (chunks of 32 tokens)."""
+    if M == 1:
+        return "gemv_w4a16_m1_kernel"
+    if M <= 8:
+        return "gemv_w4a16_warp_kernel"
+    if M <= 24 or (M <= 32 and N >= 32768):
+        return "gemv_w4a16_strip_kernel"
+    return "gemv_w4a16_tc_kernel" if M <= 32 else "gemv_w4a16_tc_kernel / strip / warp per 32-token chunk"
+
+
 def bench_gemv(pkg, args):
     stream = torch.cuda.Stream()
     for K, N in SHAPES:
@@ -93,7 +104,7 @@ def bench_gemv(pkg, args):
                 return
             t = time_graph(lambda: [lin(x) for lin in lins], 5, stream) / copies
             byt = w4_bytes(N, K) + 2 * M * (K + N)
-            print(json.dumps({"kernel": "gemv_w4a16_m1_kernel" if M == 1 else ("gemv_w4a16_warp_kernel" if M <= 16 else "gemv_w4a16_tc_kernel"), "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
+            print(json.dumps({"kernel": w4a16_kernel_name(M, N), "K": K, "N": N, "M": M, "us": round(t * 1e6, 2),
                               "GBs": round(byt / t / 1e9, 1), "frac_of_measured_hbm": round(byt / t / 1e9 / peak_hbm(), 3)}),
                   flush=True)
         del lins

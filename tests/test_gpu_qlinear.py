@@ -102,14 +102,18 @@ def test_w4a16_many_tokens_tensor_core_gemm(M, K, N):
     assert rel_err(got, orc.linear(x, dense)) < TOL_BF16
 
 
-@pytest.mark.parametrize("M", [9, 16, 17, 32, 33, 64])
-@pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 400), (14336, 512)])
-def test_w4a16_decode_gemm_on_tensor_memory(M, K, N):
-    """17..64 tokens take the tensor-memory decode GEMM (codes unpacked to 128 + q,
-    scale and zero point applied per group by the epilogue, channel tiles split
-    over K and finished by the last contributor), 9..16 the warp kernel's
-    two-token-tile form: against dequantise-then-matmul within 1e-2 relative; two
-    calls in a row give identical bits."""
+@pytest.mark.parametrize("M", [9, 16, 17, 24, 32, 33, 40, 64])
+@pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 400), (14336, 512), (512, 32808)])
+def test_w4a16_decode_gemm_9_to_64_tokens(M, K, N):
+    """9..64 tokens go in equal chunks of up to 32.  Chunks of 9..24 tokens (25..32 on a
+    weight of 32768 rows or more, or whose rows are no multiple of 16) take the strip
+    kernel (a warp multiplies 64 or 32 rows by all tokens on the warp MMA; the K slices
+    of a CTA are added through shared memory, strip sets cut between CTAs through partial
+    tiles and a counter); chunks of 25..32 tokens on smaller weights take the
+    tensor-memory decode GEMM (codes unpacked to 128 + q, scale and zero point applied per
+    group by the epilogue).  The shapes cut strip sets inside and between CTAs, leave the
+    last set short of strips, and leave the last tile short of rows.  Against
+    dequantise-then-matmul within 1e-2 relative; two calls in a row give identical bits."""
     rng = np.random.default_rng(8)
     qw, scales, qz = make_w4a16(rng, N, K)
     lin = pkg().QuantLinear.from_w4a16_gptq(qw, scales, qz, N, K, 128)
