@@ -271,14 +271,15 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     // and needs a pass per 16 tokens).  Measured on the largest shape: 343 us per pass against
     // 155 us per 16-token pass of the warp kernel, so it pays from 17 tokens.
     // More than 8 tokens go in chunks of up to 32:
-    //   9..24 tokens (and 25..32 on a weight of 32768 rows or more): the strip kernel - a warp multiplies
+    //   9..24 tokens (and 25..32 on a weight of 24576 rows or more): the strip kernel - a warp multiplies
     //     64 or 32 rows by all tokens, so the activations it loads serve several weight blocks and the
     //     codes are unpacked once for every token.  On the largest shape it takes 96 / 113 / 150 us for
     //     16 / 24 / 32 tokens; the warp kernel needs 155 us per 16 tokens.
-    //   25..32 tokens on the layer shapes: the tensor-memory decode GEMM, whose pass costs the same
+    //   25..32 tokens on narrower weights: the tensor-memory decode GEMM, whose pass costs the same
     //     whatever the token count (170 us on the largest shape, 15 / 26 / 27 us on 4096 x 4096,
     //     4096 x 14336, 14336 x 4096 against the strip kernel's 17 / 29 / 30 us).
     static const bool strip_off = getenv("AB2_GEMV_NO_STRIP") != nullptr;
+    static const int strip_wide_n = getenv("AB2_STRIP_WIDE_N") ? atoi(getenv("AB2_STRIP_WIDE_N")) : 24576;
     if constexpr (EPI != W4_EPI_F32_PEER) {
         if (M >= 9 && !norm_w) {
             const bool tc_ok = w->N % 16 == 0;
@@ -290,7 +291,7 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
                 __nv_bfloat16 *yp = EPI == W4_EPI_F32 ? (__nv_bfloat16 *)((float *)y + (size_t)m0 * out_n)
                                                       : (__nv_bfloat16 *)y + (size_t)m0 * out_n;
                 const __nv_bfloat16 *rp = resid ? (const __nv_bfloat16 *)resid + (size_t)m0 * out_n : nullptr;
-                if (!strip_off && mv >= 9 && (mv <= 24 || w->N >= 32768 || !tc_ok)) {
+                if (!strip_off && mv >= 9 && (mv <= 24 || w->N >= strip_wide_n || !tc_ok)) {
                     cudaError_t e;
                     // token tiles, tiles per strip, strips x K slices of a CTA
                     switch ((mv + 7) / 8) {

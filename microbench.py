@@ -84,7 +84,7 @@ def w4a16_kernel_name(M, N):
         return "gemv_w4a16_m1_kernel"
     if M <= 8:
         return "gemv_w4a16_warp_kernel"
-    if M <= 24 or (M <= 32 and N >= 32768):
+    if M <= 24 or (M <= 32 and N >= 24576):
         return "gemv_w4a16_strip_kernel"
     return "gemv_w4a16_tc_kernel" if M <= 32 else "gemv_w4a16_tc_kernel / strip / warp per 32-token chunk"
 

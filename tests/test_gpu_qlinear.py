@@ -106,7 +106,7 @@ def test_w4a16_many_tokens_tensor_core_gemm(M, K, N):
 @pytest.mark.parametrize("K,N", [(512, 256), (4096, 4096), (1024, 400), (14336, 512), (512, 32808)])
 def test_w4a16_decode_gemm_9_to_64_tokens(M, K, N):
     """9..64 tokens go in equal chunks of up to 32.  Chunks of 9..24 tokens (25..32 on a
-    weight of 32768 rows or more, or whose rows are no multiple of 16) take the strip
+    weight of 24576 rows or more, or whose rows are no multiple of 16) take the strip
     kernel (a warp multiplies 64 or 32 rows by all tokens on the warp MMA; the K slices
     of a CTA are added through shared memory, strip sets cut between CTAs through partial
     tiles and a counter); chunks of 25..32 tokens on smaller weights take the
