@@ -106,6 +106,7 @@ SIGNATURES = {
     "ab2_model_rope_tables": ([_p, _pp, _pp], _i),
     "ab2_model_forward": ([_p, _p, _p, _i, _i, _i, _p, _i, _p, _p, _p], _i),
     "ab2_model_decode_step": ([_p, _p, _p, _i, _i, _p, _p, _p], _i),
+    "ab2_model_decode_step_host": ([_p, _p, _p, _i, _i, _p, _p], _i),
     "ab2_model_step_trace": ([_p, _p, _i, _p], _i),
     "ab2_model_forward_rows": ([_p, _p, _p, _i, _p, _i, _i, _p, _p, _p], _i),
     "ab2_model_decode_step_rows": ([_p, _p, _p, _p, _i, _p, _p, _p], _i),

@@ -66,6 +66,9 @@ struct ab2_model {
     // one sequence, one token: the whole step as one persistent kernel (null when not eligible)
     ab2::PersistentStep *persistent;
     std::vector<ab2::PsLayerDesc> ps_layers;
+    // device copies of the token ids and greedy tokens of ab2_model_decode_step_host
+    uint32_t *host_step_ids, *host_step_out;
+    int host_step_rows;
 };
 
 namespace ab2 {
@@ -398,6 +401,7 @@ AB2_API int ab2_model_destroy(ab2_model *m) {
     cudaFree(m->x); cudaFree(m->xn); cudaFree(m->qkv); cudaFree(m->attn); cudaFree(m->proj);
     cudaFree(m->gu); cudaFree(m->hid); cudaFree(m->positions); cudaFree(m->lg_local); cudaFree(m->lg_all); cudaFree(m->proj32);
     if (m->positions_host) cudaFreeHost(m->positions_host);
+    cudaFree(m->host_step_ids); cudaFree(m->host_step_out);
     delete m;
     return AB2_OK;
 }
@@ -673,5 +677,33 @@ AB2_API int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_
     }
     AB2_CUDA(cudaGraphLaunch(it->second.exec, s));
     for (int i = 0; i < nrows; ++i) kv->lens_host[kv_row_host(kv, row0, i)] += 1;
+    return AB2_OK;
+}
+
+// The same step for a caller that holds its tokens on the host (the serving loop of the
+// reference does: InferenceEngine::decode_sessions takes and returns host tokens,
+// crates/aarambh-studio-inference/src/engine.rs:323-355): ids in, greedy tokens out, one call,
+// one wait.  The device copies live in the model, so every call replays the same graph.
+AB2_API int ab2_model_decode_step_host(ab2_model *m, ab2_kv *kv, const uint32_t *ids_host, int row0, int nrows,
+                                       uint32_t *argmax_host, ab2_stream stream) {
+    AB2_REQUIRE(m && kv && ids_host && argmax_host, AB2_ERR_BAD_ARG, "null argument");
+    AB2_REQUIRE(nrows >= 1, AB2_ERR_BAD_ARG, "nrows must be at least 1, got %d", nrows);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (m->host_step_rows < nrows) {
+        AB2_CUDA(cudaStreamSynchronize(s));  // a step in flight may still use the old buffers
+        cudaFree(m->host_step_ids);
+        cudaFree(m->host_step_out);
+        m->host_step_ids = m->host_step_out = nullptr;
+        m->host_step_rows = 0;
+        const int cap = std::max(nrows, 8);
+        AB2_CUDA(cudaMalloc((void **)&m->host_step_ids, (size_t)cap * sizeof(uint32_t)));
+        AB2_CUDA(cudaMalloc((void **)&m->host_step_out, (size_t)cap * sizeof(uint32_t)));
+        m->host_step_rows = cap;
+    }
+    AB2_CUDA(cudaMemcpyAsync(m->host_step_ids, ids_host, (size_t)nrows * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+    int rc = ab2_model_decode_step(m, kv, m->host_step_ids, row0, nrows, nullptr, m->host_step_out, stream);
+    if (rc != AB2_OK) return rc;
+    AB2_CUDA(cudaMemcpyAsync(argmax_host, m->host_step_out, (size_t)nrows * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    AB2_CUDA(cudaStreamSynchronize(s));
     return AB2_OK;
 }

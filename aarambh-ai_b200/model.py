@@ -145,6 +145,16 @@ class AarambhModel:
                                         logits.data_ptr() if logits is not None else None,
                                         argmax_dev.data_ptr() if argmax_dev is not None else None, stream_ptr()))
 
+    def decode_step_host(self, ids_host: torch.Tensor, cache: KVCache, out_host: torch.Tensor, row0: int = 0):
+        """One greedy step with the tokens in host memory: ids_host [B] int32 in, out_host [B] int32
+        out (pinned tensors make both copies asynchronous); returns when out_host is filled."""
+        if ids_host.is_cuda or out_host.is_cuda or ids_host.dtype != torch.int32 or out_host.dtype != torch.int32:
+            raise _lib.Ab2Error(-1, "decode_step_host takes int32 host tensors")
+        if out_host.numel() < ids_host.numel() or not ids_host.is_contiguous() or not out_host.is_contiguous():
+            raise _lib.Ab2Error(-1, "out_host must be contiguous and hold one token per row")
+        check(lib.ab2_model_decode_step_host(self._h, cache._h, ids_host.data_ptr(), row0, ids_host.numel(),
+                                             out_host.data_ptr(), stream_ptr()))
+
     def step_trace(self):
         """Phase timestamps (ns) of the last persistent one-row decode step as an int64
         array [3 CTAs, phases, 10]: phase start, prologue done, CTA done, barrier passed, then

@@ -385,20 +385,18 @@ def main():
         ms_per_step = dev_ms / args.steps
 
         # end to end through the host API: token ids cross PCIe both ways every step
-        ids_host = torch.empty(B, dtype=torch.int32).pin_memory()
-        out_host = torch.empty(B, dtype=torch.int32).pin_memory()
-        ids_dev = torch.empty(B, dtype=torch.int32, device="cuda")
-        out_dev = torch.empty(B, dtype=torch.int32, device="cuda")
-        ids_host.copy_(state["bufs"][state["n"] % 2].cpu())
+        host_ids = [torch.empty(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        host_ids[0].copy_(state["bufs"][state["n"] % 2].cpu())
         for b in range(B):
             cache.truncate(PROMPT, b)
+        host_n = [0]
 
         def host_step():
-            ids_dev.copy_(ids_host, non_blocking=True)
-            model.decode_step(ids_dev, cache, None, out_dev)
-            out_host.copy_(out_dev, non_blocking=True)
-            stream.synchronize()
-            ids_host.copy_(out_host)
+            # one call of the host API: ids cross to the device, the step replays, the greedy tokens
+            # cross back, the call returns when they have arrived; they are the next step's ids
+            i = host_n[0] & 1
+            model.decode_step_host(host_ids[i], cache, host_ids[i ^ 1])
+            host_n[0] += 1
 
         for _ in range(3):
             host_step()

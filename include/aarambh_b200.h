@@ -362,6 +362,13 @@ int ab2_model_forward(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int S, 
  * argmax_dev may be passed as the next ids_dev. */
 int ab2_model_decode_step(ab2_model *m, ab2_kv *kv, const uint32_t *ids_dev, int row0, int nrows,
                           void *logits_dev, uint32_t *argmax_dev, ab2_stream stream);
+/* The same step for a caller that keeps its tokens in HOST memory, as the reference's serving
+ * loop does (InferenceEngine::decode_sessions takes and returns host tokens,
+ * crates/aarambh-studio-inference/src/engine.rs:323-355): copies ids_host [nrows] to the device,
+ * replays the step, copies the greedy token of each row to argmax_host [nrows] and waits for the
+ * stream.  With pinned host buffers both copies are asynchronous and the call waits once. */
+int ab2_model_decode_step_host(ab2_model *m, ab2_kv *kv, const uint32_t *ids_host, int row0, int nrows,
+                               uint32_t *argmax_host, ab2_stream stream);
 /* The same two calls over an arbitrary set of cache rows: row i of ids / logits / argmax belongs
  * to cache row rows_host[i] (distinct rows, any order), positions are the rows' cache lengths.
  * This is what the serving batcher does each tick - every live session advances in ONE

@@ -174,6 +174,46 @@ def test_decode_step_head_dim_128_int8_kv_matches_oracle(prompt_len):
     assert pkg().device_status() == 0
 
 
+@pytest.mark.parametrize("B", [1, 3])
+def test_decode_step_with_host_tokens_equals_the_device_step(B):
+    """ab2_model_decode_step_host (ids and greedy tokens in pinned host memory, one call
+    per step, each step's tokens fed to the next) against the device-side step on a second
+    cache: the same token stream, and both equal to the argmax of the oracle's logits over
+    the sequence generated so far."""
+    cfg = dict(SMALL, d_model=512, ffn_hidden=1024, n_heads=4, n_kv_heads=2, head_dim=128, n_layers=2,
+               max_seq=256)
+    gpu, cpu, _ = build_pair(cfg, "w4a16", dtype=torch.bfloat16, max_tokens=64, batch=B, capacity=64)
+    P, steps = 9, 5
+    prompts = np.stack([prompt(cfg["vocab"], P, 40 + b) for b in range(B)])
+    host_cache = gpu.empty_kv_cache_with_capacity(P + steps + 2, batch=B, dtype="int8")
+    dev_cache = gpu.empty_kv_cache_with_capacity(P + steps + 2, batch=B, dtype="int8")
+    for b in range(B):
+        gpu.forward_with_cache(prompts[b:b + 1, :P - 1], 0, host_cache, row=b)
+        gpu.forward_with_cache(prompts[b:b + 1, :P - 1], 0, dev_cache, row=b)
+    bufs = [torch.empty(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+    bufs[0].copy_(torch.from_numpy(prompts[:, P - 1].astype(np.int32)))
+    dev = [torch.empty(B, dtype=torch.int32, device="cuda") for _ in range(2)]
+    side = torch.cuda.Stream()
+    seqs = [list(prompts[b]) for b in range(B)]
+    with torch.cuda.stream(side):
+        dev[0].copy_(bufs[0])
+        for s in range(steps):
+            gpu.decode_step_host(bufs[s & 1], host_cache, bufs[(s + 1) & 1])
+            gpu.decode_step(dev[s & 1], dev_cache, None, dev[(s + 1) & 1])
+            side.synchronize()
+            got = bufs[(s + 1) & 1].numpy().copy()
+            assert np.array_equal(got, dev[(s + 1) & 1].cpu().numpy()), s
+            for b in range(B):
+                ref = cpu.forward(np.asarray(seqs[b])[None], [0], row0=b)[0][-1]
+                top = np.sort(ref)[-2:]
+                if top[1] - top[0] > 2e-2 * np.abs(ref).max():  # a clear winner: the tokens must agree
+                    assert int(got[b]) == int(np.argmax(ref)), (s, b)
+                seqs[b].append(int(got[b]))
+    assert pkg().device_status() == 0
+    with pytest.raises(pkg().Ab2Error):
+        gpu.decode_step_host(dev[0], host_cache, bufs[0])
+
+
 def test_batched_decode_rows_match_single_row_decode_on_the_w4a16_path():
     """20 sequences decoded together (tensor-memory decode GEMM, one attention launch
     for all rows) and 12 together (warp kernel with the residual and SwiGLU
