@@ -90,32 +90,6 @@ struct W4sCursor {
     }
 };
 
-// Pairs j0 and j0 + 1 of a code word of row r (wa) and of row r + 8 (wb) as the four A registers of one
-// K step: bf16x2 of q - z ((word >> 4j) & 0x000F000F | 0x43004300 == 128 + q, plus -(128 + z), both exact).
-// Volatile, so that the place given to it between the MMAs is kept.
-template <int J0>
-__device__ __forceinline__ void w4s_unpack4(uint32_t *a, uint32_t wa, uint32_t wb, uint32_t mask,
-                                            uint32_t magic, uint32_t nza, uint32_t nzb) {
-    asm volatile(
-        "{\n"
-        " .reg .b32 t0, t1, t2, t3;\n"
-        " shr.u32 t0, %4, %6;\n"
-        " shr.u32 t1, %5, %6;\n"
-        " shr.u32 t2, %4, %7;\n"
-        " shr.u32 t3, %5, %7;\n"
-        " lop3.b32 t0, t0, %8, %9, 0xEA;\n"
-        " lop3.b32 t1, t1, %8, %9, 0xEA;\n"
-        " lop3.b32 t2, t2, %8, %9, 0xEA;\n"
-        " lop3.b32 t3, t3, %8, %9, 0xEA;\n"
-        " add.rn.bf16x2 %0, t0, %10;\n"
-        " add.rn.bf16x2 %1, t1, %11;\n"
-        " add.rn.bf16x2 %2, t2, %10;\n"
-        " add.rn.bf16x2 %3, t3, %11;\n"
-        "}\n"
-        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
-        : "r"(wa), "r"(wb), "n"(4 * J0), "n"(4 * J0 + 4), "r"(mask), "r"(magic), "r"(nza), "r"(nzb));
-}
-
 template <int EPI>
 __device__ __forceinline__ void w4s_store_frag(const float (&v)[4], int tile, int tok0, int r, int c,
                                                __nv_bfloat16 *y, const __nv_bfloat16 *resid, int N, int M) {
@@ -346,36 +320,31 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
             }
             const uint32_t xstage = xring0 + xs * XSTAGE;
             float d[RT][NT][4];
-            // Software pipeline over the 4 RT steps (B operand i, tile rt) of the group: the codes of the
-            // next step are unpacked between the MMAs of this one, so that a warp has other work to issue
-            // while the tensor pipe takes its MMAs.
-            uint32_t a[2][8];
-            uint4 xw[NT];
 #pragma unroll
-            for (int t = 0; t < NT; ++t) xw[t] = lds128(xstage + t * 512 + lane * 16);
-            w4s_unpack4<0>(a[0], wa[0][0], wb[0][0], k_mask, k_magic, nza[0], nzb[0]);
-            w4s_unpack4<2>(a[0] + 4, wa[0][0], wb[0][0], k_mask, k_magic, nza[0], nzb[0]);
+            for (int wi = 0; wi < 4; ++wi) {
+                uint4 xw[NT];
 #pragma unroll
-            for (int j = 0; j < 4 * RT; ++j) {
-                const int wi = j / RT, rt = j % RT, cur = j & 1, nxt = cur ^ 1;
-                const int nwi = (j + 1) / RT, nrt = (j + 1) % RT;
-                const bool more = j + 1 < 4 * RT;
+                for (int t = 0; t < NT; ++t) xw[t] = lds128(xstage + wi * (NT * 512) + t * 512 + lane * 16);
 #pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    if (wi == 0)
-                        mma_bf16_16816_init(d[rt][t], a[cur][0], a[cur][1], a[cur][2], a[cur][3], xw[t].x, xw[t].y);
-                    else
-                        mma_bf16_16816(d[rt][t], a[cur][0], a[cur][1], a[cur][2], a[cur][3], xw[t].x, xw[t].y);
+                for (int rt = 0; rt < RT; ++rt) {
+                    uint32_t a[8];
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        // the zero point leaves by an exact bf16x2 add: (128 + q) - (128 + z)
+                        a[2 * jj] = bf16x2_add(w4_pair_bf16(wa[rt][wi], jj, k_mask, k_magic), nza[rt]);
+                        a[2 * jj + 1] = bf16x2_add(w4_pair_bf16(wb[rt][wi], jj, k_mask, k_magic), nzb[rt]);
+                    }
+                    // the two K steps of a token tile depend on each other: all token tiles of one step first
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        if (wi == 0)
+                            mma_bf16_16816_init(d[rt][t], a[0], a[1], a[2], a[3], xw[t].x, xw[t].y);
+                        else
+                            mma_bf16_16816(d[rt][t], a[0], a[1], a[2], a[3], xw[t].x, xw[t].y);
+                    }
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) mma_bf16_16816(d[rt][t], a[4], a[5], a[6], a[7], xw[t].z, xw[t].w);
                 }
-                if (more) w4s_unpack4<0>(a[nxt], wa[nrt][nwi], wb[nrt][nwi], k_mask, k_magic, nza[nrt], nzb[nrt]);
-#pragma unroll
-                for (int t = 0; t < NT; ++t)
-                    mma_bf16_16816(d[rt][t], a[cur][4], a[cur][5], a[cur][6], a[cur][7], xw[t].z, xw[t].w);
-                if (more && nwi != wi) {
-#pragma unroll
-                    for (int t = 0; t < NT; ++t) xw[t] = lds128(xstage + nwi * (NT * 512) + t * 512 + lane * 16);
-                }
-                if (more) w4s_unpack4<2>(a[nxt] + 4, wa[nrt][nwi], wb[nrt][nwi], k_mask, k_magic, nza[nrt], nzb[nrt]);
             }
             // every lane's loads of the activation stage have been consumed by the MMAs above
             __syncwarp();
