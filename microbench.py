@@ -263,13 +263,14 @@ def bench_step(pkg, args):
     make("embedding", vocab, d)
     make("lm_head", vocab, d)
     cfg = pkg.ModelConfig(L, d, h, kvh, hd, ffn, vocab, args.ctx + 64, 1e-5, 10000.0, False)
-    model = pkg.AarambhModel(cfg, weights, dtype=torch.bfloat16, max_tokens=args.ctx)
-    cache = model.empty_kv_cache_with_capacity(args.ctx + 48, batch=1, dtype="int8")
-    prompt = torch.randint(0, vocab, (1, args.ctx), generator=torch.Generator().manual_seed(1))
+    B = args.batch
+    model = pkg.AarambhModel(cfg, weights, dtype=torch.bfloat16, max_tokens=max(args.ctx, B))
+    cache = model.empty_kv_cache_with_capacity(args.ctx + 48, batch=B, dtype="int8")
+    prompt = torch.randint(0, vocab, (B, args.ctx), generator=torch.Generator().manual_seed(1))
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
-        logits = model.forward_with_cache(prompt, 0, cache, row=0, last_only=True)
-        bufs = [pkg.dispatch.argmax(logits.view(1, -1)).clone(), torch.empty(1, dtype=torch.int32, device="cuda")]
+        first = [model.forward_with_cache(prompt[b:b + 1], 0, cache, row=b, last_only=True).view(1, -1) for b in range(B)]
+        bufs = [pkg.dispatch.argmax(torch.cat(first)).clone(), torch.empty(B, dtype=torch.int32, device="cuda")]
         n = 0
 
         def step():
@@ -281,7 +282,7 @@ def bench_step(pkg, args):
             step()
         stream.synchronize()
         if args.profile:
-            print("profiled case", L, args.ctx)
+            print("profiled case", L, args.ctx, B)
             return
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
@@ -289,7 +290,7 @@ def bench_step(pkg, args):
             step()
         b.record(stream)
         stream.synchronize()
-    print(json.dumps({"workload": f"decode step, {L} Large-shaped layers, context {args.ctx}",
+    print(json.dumps({"workload": f"decode step, {L} Large-shaped layers, context {args.ctx}, batch {B}",
                       "us_per_step": round(a.elapsed_time(b) * 1e3 / 32, 2)}), flush=True)
 
 
@@ -298,6 +299,7 @@ def main():
     ap.add_argument("what", choices=["gemv", "gemm", "attention", "prefill_attention", "step"])
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--ctx", type=int, default=512)
+    ap.add_argument("--batch", type=int, default=1, help="step: sequences decoded together")
     ap.add_argument("--m", default=None)
     ap.add_argument("--cases", default=None)
     ap.add_argument("--profile", action="store_true")
