@@ -257,7 +257,8 @@ static int forward_launches(ab2_model *m, ab2_kv *kv, const uint32_t *ids, int S
         } else if (m->fused_epilogues && T > 16) {
             // many tokens: tensor-core GEMMs, then the element-wise steps as their own launches (from 17
             // tokens on this measured faster than the residual / SwiGLU epilogues of the decode GEMM:
-            // 6330 against 6120 tok/s at 32 rows, 7360 against 6740 at 64)
+            // 6330 against 6120 tok/s at 32 rows, 7360 against 6740 at 64; with the strip kernel on the
+            // gate|up weight, 7980 against 7850 at 32 rows)
             STEP(qlinear_dispatch(L.part[3], m->attn, T, m->dtype, m->proj, s));
             STEP(launch_add_rms_norm(m->x, m->proj, L.norm2, m->xn, T, d, c.rms_eps, m->dtype, s));
             STEP(qlinear_dispatch(L.wgu, m->xn, T, m->dtype, m->gu, s));
