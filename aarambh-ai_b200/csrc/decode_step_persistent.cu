@@ -366,9 +366,13 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
             f_src = ops[f_op].wt + ((size_t)tile_lo * G + warp * base + min(warp, rem)) * W4_BLOCK_WORDS;
         }
     };
-    auto refill = [&](uint32_t stage, uint32_t bar) {
+    // `after`: a value the copy must wait for (the sums that the loads of the stage have fed): it enters the
+    // source address masked with a zero the compiler cannot see, so the copy is not issued while a load of
+    // the stage is still under way.
+    const uint32_t hidden_zero = (uint32_t)a.nops >> 30;
+    auto refill = [&](uint32_t stage, uint32_t bar, uint32_t after = 0u) {
         const uint32_t go = f_left > 0 ? 1u : 0u;
-        bulk_g2s_if(lane0 & go, stage, f_src, PS_BLOCK_BYTES, bar);
+        bulk_g2s_if(lane0 & go, stage, f_src + (after & hidden_zero), PS_BLOCK_BYTES, bar);
         if (go) {
             f_src += W4_BLOCK_WORDS;
             ++in_flight;
@@ -501,7 +505,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) decode_step_persistent_kernel(c
                     // refill this stage with the next block of the cursor (this phase or a later one)
                     __syncwarp();
                     --in_flight;
-                    refill(cur, bar);
+                    refill(cur, bar, __float_as_uint(acc_a) ^ __float_as_uint(acc_b));
                     cur += PS_BLOCK_BYTES;
                     bar += 8;
                     if (cur == ring_end) { cur = ring0; bar = bar0; parity ^= 1; }

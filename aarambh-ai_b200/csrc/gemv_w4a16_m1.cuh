@@ -320,6 +320,7 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
     }
     if (nblk == 0) return;
 
+    const uint32_t hidden_zero = (uint32_t)K & 1u;  // K is a multiple of 128
     // Opaque register copies of the constants of the nibble extraction.
     uint32_t k_lo = 0x000F000Fu, k_hi = 0x00F000F0u, k_magic = 0x64006400u;
     asm volatile("" : "+r"(k_lo), "+r"(k_hi), "+r"(k_magic));
@@ -387,8 +388,13 @@ gemv_w4a16_m1_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__res
         // The stage `cur` points into has been consumed: refill it with the two blocks STAGES stages
         // ahead (every lane's loads of it were issued above and have been consumed) and move on.
         auto next_stage = [&]() {
+            // The copy must not be issued while a load of the stage is still under way (a shared-memory load
+            // can wait behind other traffic for longer than a bulk copy out of L2 takes to land): its source
+            // address takes in the running sums, which every load of the stage has fed, masked with a zero the
+            // compiler cannot see.
+            const uint32_t held = (__float_as_uint(acc_a) ^ __float_as_uint(acc_b)) & hidden_zero;
             __syncwarp();
-            bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur, src, (uint32_t)min(to_fetch, W4M1_COPY_BLOCKS) * BLOCK_BYTES, bar);
+            bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur, src + held, (uint32_t)min(to_fetch, W4M1_COPY_BLOCKS) * BLOCK_BYTES, bar);
             src += W4M1_COPY_BLOCKS * W4_BLOCK_WORDS;
             to_fetch -= W4M1_COPY_BLOCKS;
             cur += STAGE_BYTES;

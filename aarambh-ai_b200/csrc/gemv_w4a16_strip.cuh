@@ -178,12 +178,15 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
     const int tile0 = ws * RT;  // first tile of this warp's strip inside a set
     // one group of this warp's strip into a weight stage: lane 0 arms the barrier for the blocks
     // that exist, lane t copies tile t's
-    auto fetch_w = [&](const Cursor &cu, uint32_t stage, uint32_t bar) {
+    // `after` is a value the copies must wait for: it enters their source address masked with a zero the
+    // compiler cannot see (K is a multiple of 128), so the copies cannot be issued before it is known.
+    const uint32_t hidden_zero = (uint32_t)K & 1u;
+    auto fetch_w = [&](const Cursor &cu, uint32_t stage, uint32_t bar, uint32_t after) {
         const int t0 = cu.s * (WS * RT) + tile0;
         const int nv = max(0, min(RT, tiles - t0));
         const uint32_t go = (cu.valid() && nv > 0) ? 1u : 0u;
         const uint32_t arm = go & (lane == 0 ? 1u : 0u), copy = go & (lane < nv ? 1u : 0u);
-        const uint32_t *src = wt + ((size_t)(t0 + lane) * G + cu.g) * W4_BLOCK_WORDS;
+        const uint32_t *src = wt + ((size_t)(t0 + lane) * G + cu.g) * W4_BLOCK_WORDS + (after & hidden_zero);
         asm volatile(
             "{\n"
             " .reg .pred p, q;\n"
@@ -203,7 +206,7 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
     wcur.seek(s_first, u0, u1, G, wk);
 #pragma unroll
     for (int j = 0; j < W4S_WSTAGES; ++j) {
-        fetch_w(wcur, wring0 + j * WSTAGE, wbar0 + j * 8);
+        fetch_w(wcur, wring0 + j * WSTAGE, wbar0 + j * 8, 0u);
         if (wcur.valid()) wcur.next(u0, u1, G, wk);
     }
 
@@ -216,10 +219,11 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
     // a row holds k = 8p ..: it is B operand p % 4 of lane column p / 4.
     const int xpiece = lane & 15;
     const __nv_bfloat16 *xsrc[TOK_PER_WARP / 2];
-    uint32_t xdst[TOK_PER_WARP / 2];
+    uint32_t xdst[TOK_PER_WARP / 2], xbytes[TOK_PER_WARP / 2];  // rows past the last token are filled with zeros
 #pragma unroll
     for (int j = 0; j < TOK_PER_WARP / 2; ++j) {
         const int tok = ws * TOK_PER_WARP + 2 * j + (lane >> 4);
+        xbytes[j] = tok < M ? 16u : 0u;
         xsrc[j] = x + (size_t)min(tok, M - 1) * K + xpiece * 8;
         xdst[j] = (uint32_t)((xpiece & 3) * (NT * 512) + (tok >> 3) * 512 + ((tok & 7) * 4 + (xpiece >> 2)) * 16);
     }
@@ -229,8 +233,8 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
         if (xcur.valid()) {
 #pragma unroll
             for (int j = 0; j < TOK_PER_WARP / 2; ++j)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage + xdst[j]),
-                             "l"(xsrc[j] + xcur.g * 128)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(stage + xdst[j]),
+                             "l"(xsrc[j] + xcur.g * 128), "r"(xbytes[j])
                              : "memory");
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(full) : "memory");
             xcur.next(u0, u1, G, wk);
@@ -281,9 +285,15 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
                     pa[rt] = lds32(wstage + rt * W4S_BLOCK_BYTES + param_off);
                     pb[rt] = lds32(wstage + rt * W4S_BLOCK_BYTES + param_off + 32);
                 }
-                // every lane holds its words: the stage takes the group W4S_WSTAGES ahead
+                // The stage takes the group W4S_WSTAGES ahead once every lane HOLDS its words.  The loads above
+                // have only been issued (a shared-memory load can wait behind other traffic for longer than a
+                // bulk copy out of L2 takes to land), so the refill is made to wait for one word of every load:
+                // a 16-byte load completes as a whole.
+                uint32_t held = 0;
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) held ^= wa[rt][0] ^ wb[rt][0] ^ pa[rt] ^ pb[rt];
                 __syncwarp();
-                fetch_w(wcur, wstage, wbar);
+                fetch_w(wcur, wstage, wbar, held);
                 wstage += WSTAGE;
                 wbar += 8;
                 if (wstage == wring_end) { wstage = wring0; wbar = wbar0; wparity ^= 1; }

@@ -191,6 +191,7 @@ gemv_w4a16_warp_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__r
     pdl_launch_dependents();
     if (nblk == 0) return;
 
+    const uint32_t hidden_zero = (uint32_t)K & 1u;  // K is a multiple of 128
     // Opaque register copies of the two constants of the nibble extraction.
     uint32_t k_mask = 0x000F000Fu, k_magic = 0x43004300u;
     asm volatile("" : "+r"(k_mask), "+r"(k_magic));
@@ -273,10 +274,16 @@ gemv_w4a16_warp_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__r
                 acc[t][3] = fmaf(sb, d[t][3] + dz[t][3], acc[t][3]);
             }
 
-            // Refill this stage with the block W4W_STAGES ahead: every lane's loads of
-            // it were issued at the top of the step and have been consumed above.
+            // Refill this stage with the block W4W_STAGES ahead.  The copy must not be issued while a
+            // load of the stage is still under way (a shared-memory load can wait behind other traffic
+            // for longer than a bulk copy out of L2 takes to land): its source address takes in the
+            // running sums, which every load of the stage has fed, masked with a zero the compiler
+            // cannot see.
+            uint32_t held = 0;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) held ^= __float_as_uint(acc[t][0]) ^ __float_as_uint(acc[t][2]);
             __syncwarp();
-            bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur, src, BLOCK_BYTES, bar);
+            bulk_g2s_if(lane0 & (to_fetch > 0 ? 1u : 0u), cur, src + (held & hidden_zero), BLOCK_BYTES, bar);
             src += W4_BLOCK_WORDS;
             --to_fetch;
             cur += BLOCK_BYTES;
