@@ -1,8 +1,8 @@
 """Tensor-parallel decoder against the single-GPU decoder (needs 2 GPUs; skipped
 otherwise): same seeded weights, sharded over 2 ranks, logits within 1e-2
 relative and the same greedy tokens - once with the partial sums exchanged over
-NVLink peer memory, once through NCCL; plain launches, graph-replayed steps and
-three rows decoded together."""
+NVLink peer memory, once through NCCL; plain launches, graph-replayed steps,
+three rows decoded together and a 20-token prompt."""
 import os
 import socket
 
@@ -82,6 +82,11 @@ def _run(model, steps=6):
             model.decode_step(btok, bcache, bout, None)
             side.synchronize()
         logits.extend(bout.float().cpu().numpy())
+    # a 20-token prompt (more than 16 tokens: partial sums through the collective library, the
+    # SwiGLU and f32 epilogues of the 9..32-token GEMM)
+    long_ids = torch.randint(0, CFG["vocab"], (1, 20), generator=torch.Generator().manual_seed(5))
+    lcache = model.empty_kv_cache_with_capacity(32, dtype="int8")
+    logits.append(model.forward_with_cache(long_ids, 0, lcache, last_only=True).float().cpu().numpy().ravel())
     return np.stack(logits), toks
 
 
