@@ -169,7 +169,7 @@ gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap wmap, const float *__restr
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         raw[half][i] = *reinterpret_cast<const uint4 *>(wrow + (((4 * half + 2 * hsel + i) ^ (t & 7)) << 4));
-                bar_arrive(&sh->wempty[ws]);
+                bar_arrive_after(&sh->wempty[ws], raw[0][0].x ^ raw[0][1].x ^ raw[1][0].x ^ raw[1][1].x, (uint32_t)K & 1u);
 #pragma unroll
                 for (int half = 0; half < 2; ++half, ++suse) {
                     const int s = suse % TC_STAGES;

@@ -190,7 +190,7 @@ gemm_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
 #pragma unroll
                 for (int i = 0; i < 4; ++i) pw[i] = *reinterpret_cast<const uint4 *>(bw + r * 16 + i * 4);
                 const uint32_t pr = bw[256 + r];
-                bar_arrive(&sh->wempty[ws]);
+                bar_arrive_after(&sh->wempty[ws], pw[0].x ^ pw[1].x ^ pw[2].x ^ pw[3].x ^ pr, (uint32_t)K & 1u);
                 const uint32_t sc2 = __byte_perm(pr, pr, 0x1010);  // bf16x2 (scale, scale)
                 const uint32_t nz2 = __byte_perm(pr, pr, 0x3232);  // bf16x2 -(128 + z)
 #pragma unroll

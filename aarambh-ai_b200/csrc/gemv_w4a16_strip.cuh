@@ -356,9 +356,14 @@ gemv_w4a16_strip_kernel(const uint32_t *__restrict__ wt, const __nv_bfloat16 *__
                     for (int t = 0; t < NT; ++t) mma_bf16_16816(d[rt][t], a[4], a[5], a[6], a[7], xw[t].z, xw[t].w);
                 }
             }
-            // every lane's loads of the activation stage have been consumed by the MMAs above
+            // The stage is handed back once every load of it has returned: the address of the arrival takes
+            // in the sums that the last loads of every token tile have fed (masked with the hidden zero).
+            uint32_t xheld = 0;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) xheld ^= __float_as_uint(d[RT - 1][t][0]);
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(xempty0 + xs * 8) : "memory");
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(xempty0 + xs * 8 + (xheld & hidden_zero)) : "memory");
             xs_prev = xs;
             xparity_prev = xparity;
             if (++xs == W4S_XSTAGES) { xs = 0; xparity ^= 1; }

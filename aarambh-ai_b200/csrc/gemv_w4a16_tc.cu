@@ -247,7 +247,7 @@ gemv_w4a16_tc_kernel(const uint32_t *__restrict__ wt, const __grid_constant__ CU
             const uint32_t nz2 = __byte_perm(pr, pr, 0x3232);  // bf16x2 -(128 + zero) of this channel
             // one arrival per warp: arrivals on one mbarrier serialise on its word
             __syncwarp();
-            if (lane == 0) bar_arrive(&sh->wempty[q][ws]);
+            if (lane == 0) bar_arrive_after(&sh->wempty[q][ws], p0.x ^ p1.x ^ pr, (uint32_t)K & 1u);
             const uint32_t suse = 2 * use + half;
             const int s = suse % DG_STAGES;
             if (!bar_wait(&sh->sempty[s], ((suse / DG_STAGES) & 1) ^ 1, failed)) break;

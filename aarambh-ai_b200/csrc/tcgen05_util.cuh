@@ -20,6 +20,14 @@ __device__ __forceinline__ void bar_init(uint64_t *b, uint32_t count) {
 __device__ __forceinline__ void bar_arrive(uint64_t *b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(sptr(b)) : "memory");
 }
+// Arrival that hands a shared-memory slot back to a producer of asynchronous copies.  The arrival
+// must not leave while a load of the slot is still under way (the copy that follows it may land
+// first): `held` is a value every such load has fed, `hidden_zero` a zero the compiler cannot see
+// (derived from a kernel argument); the address of the arrival takes in held & hidden_zero, so the
+// instruction waits for the loads.
+__device__ __forceinline__ void bar_arrive_after(uint64_t *b, uint32_t held, uint32_t hidden_zero) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(sptr(b) + (held & hidden_zero)) : "memory");
+}
 __device__ __forceinline__ void bar_expect_tx(uint64_t *b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(sptr(b)), "r"(bytes) : "memory");
 }
