@@ -261,6 +261,60 @@ def cpu_baseline_record(cfg, steps, warmup):
                       "dense f32 weights as the reference holds them after load"}
 
 
+def cpu_ops_record():
+    """Per-operator CPU legs of the microbenchmark configurations (`--cpu-ops`): the oracle's
+    restatement of what the reference's CPU path does per call, on all host cores.  Weight-only
+    quantised linear: the reference dequantises to dense f32 at load, so a call is a dense f32
+    product (strict-order scalar sums, the oracle's parity definition) - W4A16 shapes at 1, 4 and 16
+    tokens, 2048 tokens on the smallest shape only.  Decode attention: f32 KV cache, one task per
+    (sequence, head), for 1 and 8 sequences of 4096 and 16384 cached tokens.  The other corners of
+    the sweeps are listed as skipped: they take minutes on a CPU."""
+    import numpy as np
+    from oracle import oracle as orc
+    orc.use_all_cores()
+    rng = np.random.default_rng(2)
+    ops = []
+
+    def timed(fn, budget_s=1.5):
+        fn()
+        n, t0 = 0, time.perf_counter()
+        while True:
+            fn()
+            n += 1
+            dt = time.perf_counter() - t0
+            if dt > budget_s or n >= 20:
+                return dt / n
+
+    for K, N in [(4096, 4096), (4096, 14336), (14336, 4096), (4096, 128256)]:
+        w = rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02)
+        for M in (1, 4, 16, 2048):
+            if M == 2048 and (K, N) != (4096, 4096):
+                ops.append({"op": "linear", "K": K, "N": N, "tokens": M, "skipped": "too slow on a CPU"})
+                continue
+            x = rng.standard_normal((M, K), dtype=np.float32)
+            dt = timed(lambda: orc.linear(x, w))
+            ops.append({"op": "linear", "K": K, "N": N, "tokens": M, "ms": round(dt * 1e3, 3),
+                        "dense_f32_GBs": round(N * K * 4 / dt / 1e9, 1), "GFLOPs": round(2.0 * M * N * K / dt / 1e9, 1)})
+        del w
+    h, kvh, hd = 32, 8, 128
+    for B in (1, 8, 64):
+        for ctx in (4096, 16384, 32768):
+            if B > 8 or ctx > 16384:
+                ops.append({"op": "decode attention", "sequences": B, "context": ctx, "skipped": "too slow on a CPU"})
+                continue
+            q = rng.standard_normal((B, h, hd), dtype=np.float32)
+            kc = rng.standard_normal((B, ctx, kvh, hd), dtype=np.float32)
+            vc = rng.standard_normal((B, ctx, kvh, hd), dtype=np.float32)
+            lens = np.full(B, ctx, np.int32)
+            dt = timed(lambda: orc.attention_decode_gqa(q, kc, vc, lens, 1.0 / np.sqrt(hd)))
+            ops.append({"op": "decode attention", "sequences": B, "context": ctx, "ms": round(dt * 1e3, 3),
+                        "f32_kv_GBs": round(2.0 * B * ctx * kvh * hd * 4 / dt / 1e9, 1)})
+            del kc, vc
+    return {"cpu_ops": ops, "cores": orc.num_threads(), "kind": "port",
+            "what": "oracle restatement of the reference's CPU path per call: dense f32 product after load-time "
+                    "dequantisation, f32 KV decode attention"}
+
+
 def decode_timer(torch, model, cache, pkg, B, stream, dist, world):
     """Returns (step, time_block): `step` runs one graph-replayed decode step with on-device
     sampling; `time_block(k)` times k steps with CUDA events on the launching stream, bracketed
@@ -313,6 +367,8 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=12)
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     ap.add_argument("--skip-extra", action="store_true", help="omit the batch-32 and prefill sub-records")
+    ap.add_argument("--cpu-ops", action="store_true",
+                    help="time the CPU legs of the per-operator microbenchmarks (no GPU) and print them as one JSON line")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -320,6 +376,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     cfg = LARGE
     B = args.batch
+
+    if args.cpu_ops:
+        if rank == 0:
+            print(json.dumps(cpu_ops_record()))
+        return 0
 
     if args.impl == "reference":
         # The reference's CPU path, restated (oracle/): no GPU, none of this repository's kernels.
