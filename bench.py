@@ -506,7 +506,7 @@ def main():
                      "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                      "traffic": round(gemv_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
                      "traffic_source": "ncu dram read+write of this kernel on one token, divided by its algorithmic "
-                                       "bytes (ratio 1.014), times the bytes an average launch of the step streams",
+                                       "bytes (ratio 1.013), times the bytes an average launch of the step streams",
                      "peak_source": "measured" if peaks else "fallback",
                      "launches_per_step": gemv_launches, "bytes_per_launch": round(gemv_bytes)},
         "e2e": {"value": round(B / e2e_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": 4 * B,
