@@ -61,7 +61,7 @@ def kv_bytes_per_token(c):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of gemv_w4a16_m1_kernel divided by its
-# algorithmic bytes, from ncu captures of the kernel on one token: 283.18 MB against 279.4 MB on
+# algorithmic bytes, from ncu captures of the kernel on one token: 283.10 MB against 279.4 MB on
 # a 4096 x 128256 weight, and the in-step gate|up shape (4096 x 28672).  The kernel streams
 # every weight block exactly once whatever the shape, so traffic grows in proportion to the bytes.
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 283.10 / 279.4
