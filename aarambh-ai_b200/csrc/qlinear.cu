@@ -257,14 +257,16 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     // finishing of cut tiles.  One 16-row tile per CTA (G / 8 blocks per warp) keeps every cut inside a
     // CTA (finished through shared memory; a tile cut between CTAs goes through partial sums and a
     // counter in L2) and halves the blocks a warp walks: taken whenever it fits the resident CTAs and
-    // leaves a warp at least 4 blocks and every SM a CTA (the Large block's qkv, o and down projections:
-    // 557 -> 592 tok/s; the 768-row qkv shard of an 8-way split would occupy 48 SMs this way).
+    // leaves a warp at least 4 blocks and the SMs at least 1.7 CTAs each (the Large block's qkv, o and
+    // down projections, 384 and 256 tiles: 557 -> 592 tok/s.  With fewer tiles the SMs that hold two CTAs
+    // set the time while the others idle: the 224-tile gate|up shard of an 8-way split ran the whole step
+    // at 470 tok/s this way against 535 with equal ranges, same box, same run).
     // Large weights keep equal ranges over every resident CTA: for them balance across SMs matters more
     // (one tile set per CTA on the gate|up weight: 488 tok/s).
     static const bool align_off = getenv("AB2_GEMV_ALIGN") != nullptr && atoi(getenv("AB2_GEMV_ALIGN")) == 0;
     const int G = w->K / 128;
     int grid = (int)std::min<long long>(sc.max_ctas, std::max<long long>(1, (total / 8 + W4W_WARPS - 1) / W4W_WARPS));
-    if (!align_off && G % W4W_WARPS == 0 && G / W4W_WARPS >= 4 && tiles <= sc.max_ctas && tiles >= device_sm_count()) grid = tiles;
+    if (!align_off && G % W4W_WARPS == 0 && G / W4W_WARPS >= 4 && tiles <= sc.max_ctas && tiles * 10 >= device_sm_count() * 17) grid = tiles;
     const uint32_t *wt = (const uint32_t *)w->codes;
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
     // 17..64 tokens: the tensor-memory decode GEMM, 32 tokens per pass (the codes are unpacked once
