@@ -269,10 +269,6 @@ static int launch_w4a16_stream(const ab2_qweight *w, const void *x, int M, void 
     if (!align_off && G % W4W_WARPS == 0 && G / W4W_WARPS >= 4 && tiles <= sc.max_ctas && tiles * 10 >= device_sm_count() * 17) grid = tiles;
     const uint32_t *wt = (const uint32_t *)w->codes;
     const int out_n = EPI == W4_EPI_SWIGLU ? w->N / 2 : w->N;
-    // 17..64 tokens: the tensor-memory decode GEMM, 32 tokens per pass (the codes are unpacked once
-    // per pass whatever the token count; the warp kernel re-reads its activations for every block
-    // and needs a pass per 16 tokens).  Measured on the largest shape: 343 us per pass against
-    // 155 us per 16-token pass of the warp kernel, so it pays from 17 tokens.
     // More than 8 tokens go in chunks of up to 32:
     //   9..24 tokens (and 25..32 on a weight of 24576 rows or more): the strip kernel - a warp multiplies
     //     64 or 32 rows by all tokens, so the activations it loads serve several weight blocks and the
@@ -414,8 +410,8 @@ int qlinear_i8_tc(const ab2_qweight *w, const void *x, int M, void *y, cudaStrea
 
 int qlinear_dispatch(const ab2_qweight *w, const void *x, int M, ab2_dtype dtype, void *y, cudaStream_t s) {
     if (qlinear_w4a16_mma_eligible(w, dtype)) {
-        // Few tokens: HBM-bound GEMV on the warp MMA (16 tokens per pass).  The
-        // tcgen05 GEMM tiles 128 output channels per CTA, which leaves most SMs
+        // Up to 64 tokens: the HBM-bound decode kernels (one token, 2..8 tokens, chunks of 9..32
+        // tokens).  The tcgen05 GEMM tiles 128 output channels per CTA, which leaves most SMs
         // idle until the token count supplies the parallelism.
         if (M <= 64) return qlinear_w4a16_mma(w, x, M, y, s);
         return qlinear_w4a16_tc(w, x, M, y, s);
