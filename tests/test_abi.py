@@ -35,3 +35,20 @@ def test_version_and_error_string():
     p = pkg()
     assert p.lib.ab2_version() >= 100
     assert isinstance(p.lib.ab2_last_error(), bytes)
+
+
+def test_null_arguments_are_refused_before_any_device_work():
+    """Entry points validate their pointers first: a null handle or buffer gives AB2_ERR_BAD_ARG
+    (-7) and a message, on a machine without a GPU as well."""
+    p = pkg()
+    calls = {
+        "ab2_qlinear_forward": (None, None, 1, 2, None, None),
+        "ab2_qweight_dequant": (None, None, 0, None),
+        "ab2_swiglu": (None, None, None, 8, 2, None),
+        "ab2_model_decode_step": (None, None, None, 0, 1, None, None, None),
+        "ab2_model_decode_step_host": (None, None, None, 0, 1, None, None),
+        "ab2_device_status": (None,),
+    }
+    for name, args in calls.items():
+        assert getattr(p.lib, name)(*args) == -7, name
+        assert b"null" in p.lib.ab2_last_error(), name
